@@ -23,12 +23,14 @@ from .manager import GroupSpec
 @dataclass(frozen=True)
 class KVLayerSpec:
     """``value_dim``: values have a size of their own (None: the keys' ``head_dim``); keys and values
-    are then two device tensors, ``[layers, pages + 1, kv_heads, page_size, head_dim | value_dim]``."""
+    are then two device tensors, ``[layers, pages + 1, kv_heads, page_size, head_dim | value_dim]``.
+    ``keep_first``: with a window, the sequence's first ``keep_first`` tokens stay readable as well."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
+    keep_first: int = 0
 
     @property
     def split(self) -> bool:
@@ -90,7 +92,8 @@ class CacheLayout:
         self.groups: list[GroupLayout] = []
         for spec, ids in buckets.items():
             if isinstance(spec, (KVLayerSpec, LatentLayerSpec)):
-                gs = GroupSpec("window", spec.window) if spec.window else GroupSpec("full")
+                gs = (GroupSpec("window", spec.window, getattr(spec, "keep_first", 0)) if spec.window
+                      else GroupSpec("full"))
             elif isinstance(spec, StateLayerSpec):
                 gs = GroupSpec("state")
             else:
@@ -148,7 +151,8 @@ class CacheLayout:
         for i, gi in enumerate(self.paged_groups):
             window = self.groups[gi].spec.window
             if window:
-                cap = max_num_seqs * (-(-(window + max_step_tokens) // page_size) + 2)
+                kept = -(-self.groups[gi].spec.keep_first // page_size)
+                cap = max_num_seqs * (-(-(window + max_step_tokens) // page_size) + 2 + kept)
                 counts[i] = min(equal, cap)
                 spent += counts[i] * per[i]
             else:

@@ -4,7 +4,8 @@ Layers are put into *groups* by what they need from the cache:
 
 * ``full``   -- every key and value of the request stays (Qwen3 dense: one such group);
 * ``window`` -- only the last ``window`` keys are read, so pages that the window has
-  passed are given back while the request is still running;
+  passed are given back while the request is still running (except the pages that hold the
+  sequence's first ``keep_first`` tokens, when the group keeps those readable);
 * ``state``  -- a fixed-size slot per request (recurrent or convolution state), no pages.
 
 Each paged group has pages of its own (its own allocator and device tensors) and
@@ -39,6 +40,7 @@ class GroupSpec:
 
     kind: str
     window: int | None = None
+    keep_first: int = 0  # a window group: the first tokens of a sequence that stay readable too
 
     def __post_init__(self) -> None:
         if self.kind not in ("full", "window", "state"):
@@ -229,7 +231,8 @@ class CacheManager:
                 continue
             # the next query sits at position >= end and reads keys > end - window
             first_needed = max(0, end - group.window + 1)
-            for idx in range(min(first_needed // self.page_size, len(table))):
+            kept_pages = -(-group.keep_first // self.page_size)  # pages that hold a kept first token
+            for idx in range(kept_pages, min(first_needed // self.page_size, len(table))):
                 if table[idx] != FREED:
                     alloc.release(table[idx])
                     table[idx] = FREED

@@ -1,5 +1,6 @@
 from .engine_config import EngineConfig, canonical_dtype
 from .logesun_config import LogesunConfig
+from .medilix_config import MedilixConfig
 from .puladra_config import PuladraConfig
 from .model_config import ConfigError, Qwen3Config
 from .registry import (
@@ -23,6 +24,7 @@ __all__ = [
     "EngineConfig",
     "LayerRun",
     "LogesunConfig",
+    "MedilixConfig",
     "ModelSpec",
     "PartSpec",
     "PuladraConfig",

@@ -40,7 +40,10 @@ class LayerRun:
     before this entry runs (a looped stack that is fed its input again).  ``add_row``
     ``(table, row)``: row ``row`` of the model's shared table ``table`` (``ModelSpec.shared_tables``),
     one vector of the model's width, is added to every token of the stream right before this
-    entry runs (a learned vector per pass of a loop).
+    entry runs (a learned vector per pass of a loop).  ``mix_source``: the name of a shared table
+    ``[width, 2 * width]``; right before this entry runs the stream becomes that matrix times
+    ``[stream; embedding output]`` (a looped stack whose every pass is fed the model's input again
+    through a learned projection).
     """
 
     block: int
@@ -48,6 +51,7 @@ class LayerRun:
     writes: bool = True
     add_embedding: bool = False
     add_row: tuple[str, int] | None = None
+    mix_source: str | None = None
 
 
 @dataclass(frozen=True)
@@ -69,6 +73,10 @@ class ModelSpec:
     # model loads them into ``BuildContext.shared`` under their names, where parts (a second embedding
     # that every block reads a slice of) and run entries (``LayerRun.add_row``) find them.
     shared_tables: tuple[tuple[str, tuple[int, ...], str], ...] = ()
+    # An ``embedding`` part that makes the stream's first value from the step's tokens (and may keep
+    # state per request, e.g. the previous token).  None: a plain lookup in ``embed_name``, done by the
+    # first norm.  The part's tensors are stored under their own names (no prefix).
+    embedding: PartSpec | None = None
 
     def __post_init__(self) -> None:
         if self.logit_softcap is not None and not self.logit_softcap > 0:
@@ -85,6 +93,8 @@ class ModelSpec:
                 raise ValueError(f"run entry reads cache layer {run.cache} before any entry writes it")
             if run.add_row is not None and run.add_row[0] not in {name for name, _s, _k in self.shared_tables}:
                 raise ValueError(f"run entry adds a row of {run.add_row[0]!r}, which is no shared table of the model")
+            if run.mix_source is not None and run.mix_source not in {name for name, _s, _k in self.shared_tables}:
+                raise ValueError(f"run entry mixes through {run.mix_source!r}, which is no shared table of the model")
 
     @staticmethod
     def sequential_order(num_blocks: int) -> tuple[LayerRun, ...]:

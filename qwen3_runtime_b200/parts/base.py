@@ -1,6 +1,6 @@
 """What every part is, and the registry that finds a part class by category and kind.
 
-Categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``side_input``, ``block``.  A part is
+Categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``side_input``, ``block``, ``embedding``.  A part is
 built from a :class:`PartSpec` (its sizes and constants) and a :class:`BuildContext`
 (dtype, device, kernel table); it declares its tensors with :meth:`Part.param_specs`
 (names relative to the part's own prefix) and receives them, already on the device,
@@ -17,7 +17,7 @@ import torch
 
 from ..config.spec import PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "side_input", "block")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "side_input", "block", "embedding")
 
 
 @dataclass(frozen=True)
@@ -162,15 +162,32 @@ class ResidualStream:
     is fed its input again); the next norm does it and clears the flag.
     ``add_vector``: a float32 vector of the model's width that the next norm adds to every row of
     the sum (and then forgets): a learned offset per pass of a loop.
+    ``pending_more``: a second sublayer output ``[tokens, hidden]`` in the compute dtype that is added
+    together with ``pending`` (a block whose mixer and feed-forward read the same input).
+
+    A stream may also be started by an ``embedding`` part (:meth:`started`): ``resid`` then holds the
+    embedding output already, and ``source_pair`` (if the model asked for it) is a buffer
+    ``[tokens, 2 * hidden]`` in the compute dtype whose right half holds the embedding output, the left
+    half being free for the folded stream (the operand of a projection of ``[stream; embedding output]``).
     """
 
-    def __init__(self, num_tokens: int, hidden_size: int, *, ids: torch.Tensor, table: torch.Tensor):
+    def __init__(self, num_tokens: int, hidden_size: int, *, ids: torch.Tensor | None, table: torch.Tensor | None):
         self.num_tokens = num_tokens
         self.hidden_size = hidden_size
-        self.source: tuple[torch.Tensor, torch.Tensor] = (ids, table)
-        self.embed: tuple[torch.Tensor, torch.Tensor] | None = (ids, table)
+        self.source: tuple[torch.Tensor, torch.Tensor] | None = (ids, table) if ids is not None else None
+        self.embed: tuple[torch.Tensor, torch.Tensor] | None = self.source
         self.resid: torch.Tensor | None = None
+        self.pending_more: torch.Tensor | None = None
+        self.source_pair: torch.Tensor | None = None
         self.pending: torch.Tensor | None = None
         self.pending_norm: tuple[torch.Tensor, float] | None = None
         self.add_source = False
         self.add_vector: torch.Tensor | None = None
+
+    @classmethod
+    def started(cls, resid: torch.Tensor, source_pair: torch.Tensor | None = None) -> "ResidualStream":
+        """A stream whose first value an embedding part has computed: ``resid`` float32 ``[tokens, hidden]``."""
+        stream = cls(resid.shape[0], resid.shape[1], ids=None, table=None)
+        stream.resid = resid
+        stream.source_pair = source_pair
+        return stream

@@ -3,7 +3,9 @@
 feed-forward may be absent, and a ``side_input`` part may add something of its own to the stream
 after the sublayers.
 ``sandwich_norm``: a norm before and after each sublayer, x += norm_b(mixer(norm(x))) and
-x += norm_b(ff(norm(x))), the feed-forward being optional."""
+x += norm_b(ff(norm(x))), the feed-forward being optional.
+``parallel_norms``: mixer and feed-forward read the same stream through a norm each and are added
+together, x += mixer(norm_a(x)) + ff(norm_b(x)); the feed-forward is optional."""
 
 from __future__ import annotations
 
@@ -154,5 +156,65 @@ class SandwichNormBlock(Part):
             stream.pending_norm = self.feed_forward_out_norm.pending_scale()
 
 
+class ParallelNormsBlock(Part):
+    """x += mixer(norm_a(x)) + ff(norm_b(x)).  Both norms see the same sum, so one kernel folds what is
+    pending, takes the mean squares once and writes both normalised rows; the two sublayers' outputs
+    are left on the stream side by side and whichever norm reads the stream next adds both."""
+
+    category = "block"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.mixer = build_part("mixer", spec["mixer"], ctx)
+        self.mixer_norm = build_part("norm", spec["mixer_norm"], ctx)
+        self.children = {spec.get("mixer_prefix", "mixer."): self.mixer,
+                         spec.get("mixer_norm_prefix", "mixer_norm."): self.mixer_norm}
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.get("feed_forward") is not None:
+            self.feed_forward = build_part("feed_forward", spec["feed_forward"], ctx)
+            self.feed_forward_norm = build_part("norm", spec["feed_forward_norm"], ctx)
+            self.children.update({spec.get("feed_forward_prefix", "feed_forward."): self.feed_forward,
+                                  spec.get("feed_forward_norm_prefix", "feed_forward_norm."): self.feed_forward_norm})
+        self.entry_norm = self.mixer_norm
+        self._owners = {prefix + name: (part, name) for prefix, part in self.children.items()
+                        for name in part.param_specs()}
+
+    def exit_to(self, norms) -> None:
+        """Two outputs leave the block side by side, both finished products."""
+
+    def param_specs(self):
+        return {full: part.param_specs()[name] for full, (part, name) in self._owners.items()}
+
+    def load(self, tensors):
+        per_part: dict[int, dict] = {}
+        for full, (part, name) in self._owners.items():
+            per_part.setdefault(id(part), {})[name] = tensors[full]
+        for part in self.children.values():
+            part.load(per_part.get(id(part), {}))
+
+    def kernel_groups(self):
+        return ["norm", *[g for part in self.children.values() for g in part.kernel_groups()]]
+
+    def step_choosers(self):
+        return {name: fn for part in self.children.values() for name, fn in part.step_choosers().items()}
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def position_limit(self):
+        limits = [n for n in (part.position_limit() for part in self.children.values()) if n is not None]
+        return min(limits) if limits else None
+
+    def forward(self, stream: ResidualStream, step: StepContext, cache) -> None:
+        if self.feed_forward is None:
+            h = self.mixer_norm.add_norm(stream)
+            stream.pending = self.mixer.forward(h, step, cache)
+            return
+        h_mixer, h_ff = self.mixer_norm.add_norm(stream, second=self.feed_forward_norm)
+        stream.pending = self.mixer.forward(h_mixer, step, cache)
+        stream.pending_more = self.feed_forward.forward(h_ff, step)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel_norms", ParallelNormsBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)

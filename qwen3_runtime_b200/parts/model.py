@@ -11,6 +11,9 @@ import torch
 from ..cache.layout import CacheLayout
 from ..config.spec import ModelSpec
 from .base import BuildContext, ParamSpec, ResidualStream, StepContext, build_part
+from .norm import fold_stream
+
+EMBEDDING_CACHE = -1  # cache layer id of what the embedding part keeps per request
 
 
 class DecoderModel:
@@ -20,6 +23,10 @@ class DecoderModel:
         self.ops = ctx.ops
         self.blocks = [build_part("block", b, ctx) for b in spec.blocks]
         self.final_norm = build_part("norm", spec.final_norm, ctx)
+        self.embedding = build_part("embedding", spec.embedding, ctx) if spec.embedding is not None else None
+        self.keeps_source = any(run.mix_source is not None for run in spec.order)
+        if self.keeps_source and self.embedding is None:
+            raise ValueError("a run entry that mixes the embedding output back in needs an embedding part")
         # tell each block which norms take its output: the entry norm of whatever runs after
         # it (a block may run more than once), or the final norm
         takers: dict[int, list] = {}
@@ -42,7 +49,10 @@ class DecoderModel:
     def expected_tensors(self) -> dict[str, ParamSpec]:
         """Every stored tensor by its checkpoint name, in a fixed order."""
         s = self.spec
-        out: dict[str, ParamSpec] = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
+        if self.embedding is not None:  # the part's tensors under their own names
+            out: dict[str, ParamSpec] = dict(self.embedding.param_specs())
+        else:
+            out = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
         for name, shape, kind in s.shared_tables:
             out[name] = ParamSpec(tuple(shape), kind)
         for i, block in enumerate(self.blocks):
@@ -69,7 +79,11 @@ class DecoderModel:
         part and let go as soon as the part has taken (and possibly fused) them, so that beside
         the model's own tensors only one block's stored tensors are alive at any time."""
         s = self.spec
-        self.embed = fetch(s.embed_name).contiguous()
+        if self.embedding is not None:
+            self.embedding.load({name: fetch(name) for name in self.embedding.param_specs()})
+            self.embed = self.embedding.table
+        else:
+            self.embed = fetch(s.embed_name).contiguous()
         for name, _shape, _kind in s.shared_tables:  # before the blocks: their parts may read them
             self.ctx.shared[name] = fetch(name).contiguous()
         for i, block in enumerate(self.blocks):
@@ -81,7 +95,7 @@ class DecoderModel:
 
     def kernel_groups(self) -> list[str]:
         groups = {"norm"}
-        for part in [*self.blocks, self.final_norm]:
+        for part in [*self.blocks, self.final_norm, *([self.embedding] if self.embedding is not None else [])]:
             groups.update(part.kernel_groups())
         return sorted(groups)
 
@@ -93,6 +107,8 @@ class DecoderModel:
     # ---- cache ------------------------------------------------------------------------
     def cache_layout(self) -> CacheLayout:
         specs = {}
+        if self.embedding is not None:  # what the embedding keeps per request (the previous token)
+            specs[EMBEDDING_CACHE] = self.embedding.cache_spec()
         for run in self.spec.order:
             if run.writes:
                 specs[run.cache] = self.blocks[run.block].cache_spec()
@@ -110,8 +126,17 @@ class DecoderModel:
         """Run the step's tokens through every run entry; float32 logits ``[R, V]`` at
         ``step.logit_rows`` (None when no logits are wanted)."""
         s = self.spec
-        stream = ResidualStream(step.num_tokens, s.hidden_size, ids=step.token_ids, table=self.embed)
+        if self.embedding is not None:
+            stream = self.embedding.start(step, storage.view(EMBEDDING_CACHE), keep_source=self.keeps_source)
+        else:
+            stream = ResidualStream(step.num_tokens, s.hidden_size, ids=step.token_ids, table=self.embed)
         for run in s.order:
+            if run.mix_source is not None:
+                # stream <- M [stream; embedding output]: the sum so far, rounded to the operand type, goes
+                # into the left half of the pair buffer, whose right half the embedding part filled
+                pair = stream.source_pair
+                fold_stream(self.ops, stream, pair[:, : s.hidden_size])
+                stream.resid = self.ops.linear(pair, self.ctx.shared[run.mix_source], out_dtype=torch.float32)
             if run.add_embedding:
                 stream.add_source = True
             if run.add_row is not None:

@@ -1,6 +1,8 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, all in float32, one rounding at the end
 (qwen3_runtime/layers/ops.py:17-20; residual form :28-37).  ``weight_offset``: the stored weight
-is the deviation from this value, which is added to it when it is loaded (y = ... * (offset + w))."""
+is the deviation from this value, which is added to it when it is loaded (y = ... * (offset + w)).
+``groups`` > 1: a row is cut into that many equal consecutive parts and each is divided by its own root
+mean square (the weight still spans the whole row)."""
 
 from __future__ import annotations
 
@@ -20,6 +22,9 @@ class RMSNorm(Part):
         # the stored tensor's name after the part's prefix ("" when the prefix is the whole name)
         self.weight_name = str(spec.get("weight_name", "weight"))
         self.weight_offset = float(spec.get("weight_offset", 0.0))
+        self.groups = int(spec.get("groups") or 1)
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"rmsnorm: {self.size} elements do not split into {self.groups} equal groups")
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
@@ -38,13 +43,17 @@ class RMSNorm(Part):
         return ["norm"]
 
     def add_norm(self, stream: ResidualStream, rows: torch.Tensor | None = None,
-                 num_rows: int | None = None, normalise: bool = True) -> torch.Tensor:
+                 num_rows: int | None = None, normalise: bool = True, second: "RMSNorm | None" = None):
         """Fold what is pending into the residual sum and return its normalised rows.
 
         With ``rows`` only those rows are normalised and the residual sum is left as
         it is (the final norm before the output head).  ``normalise=False``: the rows of the sum
-        itself, rounded to the activation type (the stream as the input of a product)."""
+        itself, rounded to the activation type (the stream as the input of a product).
+        ``second``: another norm of the same size, groups and eps; the answer is then the pair
+        ``(this norm's rows, the second norm's rows)`` of the same sum, made by one kernel."""
         n = stream.num_tokens if rows is None else (num_rows if num_rows is not None else rows.numel())
+        if self.groups > 1 or second is not None or stream.pending_more is not None:
+            return self._grouped(stream, rows, n, normalise, second)
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=self.ctx.device)
         keep = rows is None
         extra = {}
@@ -76,6 +85,35 @@ class RMSNorm(Part):
             stream.add_source = False
             stream.add_vector = None
         return out
+
+
+    def _grouped(self, stream: ResidualStream, rows, n: int, normalise: bool, second):
+        """The general kernel: groups, two pending outputs, two weights."""
+        if stream.embed is not None or stream.pending_norm is not None or stream.add_source or stream.add_vector is not None:
+            raise NotImplementedError("rmsnorm: the grouped norm kernel folds pending outputs only (no embedding lookup, "
+                                      "no normalised pending output, no added rows or vectors)")
+        if second is not None and (second.size != self.size or second.groups != self.groups or second.eps != self.eps):
+            raise ValueError("rmsnorm: two norms of one sum share size, groups and eps")
+        keep = rows is None
+        out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=self.ctx.device)
+        out2 = torch.empty_like(out) if second is not None else None
+        self.ops.grouped_norm(out, self.weight if normalise else None, self.eps, self.groups, resid=stream.resid,
+                              pending=stream.pending, pending_more=stream.pending_more, rows=rows, write_resid=keep,
+                              num_rows=n, out2=out2, weight2=second.weight if second is not None else None)
+        if keep:
+            stream.pending = stream.pending_more = None
+        return out if second is None else (out, out2)
+
+
+def fold_stream(ops, stream: ResidualStream, out: torch.Tensor) -> torch.Tensor:
+    """Add what is pending to the residual sum and write the sum, rounded to ``out``'s type, into ``out``
+    (``[tokens, hidden]``, possibly a view of wider rows)."""
+    if stream.embed is not None or stream.pending_norm is not None or stream.add_source or stream.add_vector is not None:
+        raise NotImplementedError("fold_stream: the stream holds more than pending outputs")
+    ops.grouped_norm(out, None, 0.0, 1, resid=stream.resid, pending=stream.pending, pending_more=stream.pending_more,
+                     rows=None, write_resid=True, num_rows=stream.num_tokens)
+    stream.pending = stream.pending_more = None
+    return out
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -1,0 +1,96 @@
+"""Softmax attention with grouped key/value heads, a window that keeps the sequence's first tokens, a
+sink in the softmax and a gate on the heads' outputs.
+
+    q, k, v, g = W_q h, W_k h, W_v h, W_g h              (one product)
+    q, k: every head divided by its root mean square, times a weight shared by the heads (optional)
+    score(i, j) = (q_i . k_j) * scale;  i sees j <= i with i - j < window or j < keep_first
+    p_j = exp(s_j) / (exp(sink) + sum_j' exp(s_j'))      (``sink`` None: a plain softmax)
+    out = W_o (heads' outputs * sigmoid(g))              (``gate`` None: no gate)
+
+Positions do not enter the scores.  Keys and values may have unlike sizes per head.  The cache is a
+paged key/value layer whose group gives back the pages that lie wholly between the kept first tokens
+and the window.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.layout import KVLayerSpec
+from .base import BuildContext, ParamSpec, Part, StepContext, register_part
+from .linear_state import _pad_rows
+
+
+class SinkWindowAttention(Part):
+    category = "mixer"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.hidden_size = int(spec["hidden_size"])
+        self.num_heads = int(spec["num_heads"])
+        self.num_kv_heads = int(spec["num_kv_heads"])
+        self.dim = int(spec["dim"])
+        self.vdim = int(spec["vdim"])
+        self.scale = float(spec["scale"])
+        self.window = spec.get("window") or None
+        self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
+        self.sink = spec.get("sink")  # the sink's score (a number), or None
+        self.gate = spec.get("gate")  # "sigmoid" or None
+        self.qk_norm_eps = spec.get("qk_norm_eps")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.dim > 256 or self.vdim > 256:
+            raise ValueError(f"dim={self.dim}, vdim={self.vdim}: the attention kernels take sizes up to 256")
+        if self.gate not in (None, "sigmoid"):
+            raise ValueError(f"sink_window_attention: gate is 'sigmoid' or absent, not {self.gate!r}")
+        self.in_weight = self.o_weight = self.q_norm = self.k_norm = None
+        self.starts: list[int] = []
+
+    def param_specs(self):
+        H, G, D, Dv, W = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.hidden_size
+        specs = {"q": ParamSpec((H * D, W)), "k": ParamSpec((G * D, W)), "v": ParamSpec((G * Dv, W)),
+                 "o": ParamSpec((W, H * Dv))}
+        if self.gate:
+            specs["g"] = ParamSpec((H * Dv, W))
+        if self.qk_norm_eps is not None:
+            specs["q.norm"] = ParamSpec((D,), "vector")
+            specs["k.norm"] = ParamSpec((D,), "vector")
+        return specs
+
+    def load(self, tensors):
+        blocks = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.gate else [])
+        self.in_weight, self.starts = _pad_rows(blocks)
+        self.o_weight = tensors["o"].contiguous()
+        self.q_norm = tensors.get("q.norm")
+        self.k_norm = tensors.get("k.norm")
+
+    def kernel_groups(self):
+        groups = ["rope_kv", "attention_generic"]
+        groups += ["gemm_f32"] if self.ctx.dtype == torch.float32 else ["gemm_small_m", "gemm_stream"]
+        return groups
+
+    def cache_spec(self):
+        return KVLayerSpec(self.num_kv_heads, self.dim, self.window, value_dim=self.vdim, keep_first=self.keep_first)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
+        ops = self.ops
+        H, G, D, Dv = self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        s = self.starts
+        proj = ops.linear(h, self.in_weight)
+        block_table = step.block_tables[cache.paged_index]
+        ops.qk_norm_store(proj, num_heads=H, num_kv_heads=G, head_dim=D, value_dim=Dv, k_start=s[1], v_start=s[2],
+                          q_weight=self.q_norm, k_weight=self.k_norm,
+                          eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, positions=step.positions,
+                          token_seq=step.token_seq, block_table=block_table, k_pages=cache.k_pages,
+                          v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes)
+        ctx = torch.empty((h.shape[0], H * Dv), dtype=h.dtype, device=h.device)
+        gate = proj[:, s[3]:s[3] + H * Dv] if self.gate else None
+        ops.paged_attention(proj, proj.stride(0), num_heads=H, num_kv_heads=G, head_dim=D, k_pages=cache.k_pages,
+                            v_pages=cache.v_pages, block_table=block_table, token_seq=step.token_seq,
+                            positions=step.positions, out=ctx, page_size=cache.page_size, scale=self.scale,
+                            window=self.window, step=step, value_dim=Dv, keep_first=self.keep_first, sink=self.sink,
+                            gate=gate)
+        return ops.linear(ctx, self.o_weight)
+
+
+register_part("mixer", "sink_window_attention", SinkWindowAttention)

@@ -51,6 +51,117 @@ class TorchOps:
         out[:n] = ((v * torch.rsqrt(var + eps)) * weight.float()).to(out.dtype)
         return out
 
+    def grouped_norm(self, out, weight, eps, groups, *, resid, pending=None, pending_more=None, rows=None,
+                     write_resid=True, num_rows=None, out2=None, weight2=None):
+        n = out.shape[0] if num_rows is None else num_rows
+        src = rows[:n].long() if rows is not None else torch.arange(n, device=out.device)
+        H = resid.shape[1]
+        add = None
+        if pending is not None and pending.dim() == 3:
+            add = pending[0][src]
+            for p in range(1, pending.shape[0]):
+                add = add + pending[p][src]
+        elif pending is not None:
+            add = pending[src].float()
+        if pending_more is not None:
+            add = pending_more[src].float() if add is None else add + pending_more[src].float()
+        v = resid[src].float()
+        if add is not None:
+            v = v + add
+        if write_resid:
+            resid[src] = v
+        if weight is None:
+            out[:n] = v.to(out.dtype)
+            return out
+        parts = v.reshape(n, groups, H // groups)
+        unit = (parts * torch.rsqrt(parts.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, H)
+        out[:n] = (unit * weight.float()).to(out.dtype)
+        if out2 is not None:
+            out2[:n] = (unit * weight2.float()).to(out2.dtype)
+        return out
+
+    def bigram_embed(self, ids, *, embed, scale, bigram, buckets, mul_prev, mul_cur, prev_state, positions,
+                     token_seq, cu_seqlens, state_slots, num_seqs, out, copy=None):
+        T = out.shape[0]
+        tok = ids[:T].long()
+        x = embed[tok].float() * scale
+        if buckets:
+            for b in range(num_seqs):
+                t0, t1 = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+                slot = int(state_slots[b])
+                for t in range(t0, t1):
+                    if int(positions[t]) == 0:
+                        row = buckets
+                    else:
+                        prev = int(tok[t - 1]) if t > t0 else int(prev_state[slot, 0])
+                        row = (prev * mul_prev + int(tok[t]) * mul_cur) % buckets
+                    x[t] = x[t] + bigram[row].float()
+                if t1 > t0:
+                    prev_state[slot, 0] = int(tok[t1 - 1])
+        out.copy_(x)
+        if copy is not None:
+            copy.copy_(x.to(copy.dtype))
+        return out
+
+    def token_shift_mix(self, h, mu, *, state, positions, token_seq, cu_seqlens, state_slots, num_seqs):
+        T, W = h.shape
+        prev = torch.zeros((T, W), dtype=torch.float32, device=h.device)
+        for b in range(num_seqs):
+            t0, t1 = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+            slot = int(state_slots[b])
+            for t in range(t0, t1):
+                if int(positions[t]) > 0:
+                    prev[t] = h[t - 1].float() if t > t0 else state[slot]
+            if t1 > t0:
+                state[slot] = h[t1 - 1].float()
+        hf = h.float()
+        return (hf[None] + (prev - hf)[None] * mu.float()[:, None, :]).to(h.dtype)
+
+    def tanh_rows(self, x):
+        x.copy_(torch.tanh(x.float()).to(x.dtype))
+        return x
+
+    def stabilised_gates(self, zi, zf, *, i_bias, f_bias, cap, m_state, cu_seqlens, state_slots, num_seqs):
+        T, H = zi.shape
+        li = cap * torch.tanh((zi.float() + i_bias.float()) / cap)
+        lf = torch.nn.functional.logsigmoid(cap * torch.tanh((zf.float() + f_bias.float()) / cap))
+        decay = torch.empty((T, H), dtype=torch.float32, device=zi.device)
+        k_scale, m_run = torch.empty_like(decay), torch.empty_like(decay)
+        for b in range(num_seqs):
+            slot = int(state_slots[b])
+            m = m_state[slot].clone()
+            for t in range(int(cu_seqlens[b]), int(cu_seqlens[b + 1])):
+                m_new = torch.maximum(lf[t] + m, li[t])
+                decay[t] = torch.exp(lf[t] + m - m_new)
+                k_scale[t] = torch.exp(li[t] - m_new)
+                m_run[t] = m = m_new
+            m_state[slot] = m
+        return decay, k_scale, m_run
+
+    def qk_norm_store(self, proj, *, num_heads, num_kv_heads, head_dim, value_dim, k_start, v_start, q_weight, k_weight,
+                      eps, positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+        T = proj.shape[0]
+        H, G, D, Dv = num_heads, num_kv_heads, head_dim, value_dim
+
+        def unit(x, w):
+            if w is None:
+                return x
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+        q = unit(proj[:, : H * D].reshape(T, H, D).float(), q_weight)
+        proj[:, : H * D] = q.reshape(T, H * D).to(proj.dtype)
+        if not write_kv:
+            return
+        k = unit(proj[:, k_start:k_start + G * D].reshape(T, G, D).float(), k_weight).to(proj.dtype)
+        v = proj[:, v_start:v_start + G * Dv].reshape(T, G, Dv)
+        for t in range(T):
+            p = int(positions[t])
+            page = int(block_table[int(token_seq[t]), p // page_size])
+            if page < 0:
+                continue
+            k_pages[page, :, p % page_size, :] = k[t]
+            v_pages[page, :, p % page_size, :] = v[t]
+
     def silu_mul(self, gate_up, out):
         I = out.shape[-1]
         g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
@@ -81,9 +192,13 @@ class TorchOps:
 
     def decayed_state_scan(self, q, k, v, *, state, cu_seqlens, state_slots, num_seqs, decay_logits=None,
                            decay_bias=None, tau=1.0, head_decay=None, inv_freq=None, positions=None, q_scale=1.0,
-                           k_scale=1.0):
+                           k_scale=1.0, decay_mode="sigmoid_pow", token_decay=None, token_k_scale=None, bonus=None,
+                           ones_column=False):
         T, H, D = q.shape
-        Dv = v.shape[2]
+        Dv = v.shape[2] + int(ones_column)
+        vf = v.float()
+        if ones_column:
+            vf = torch.cat([vf, torch.ones((T, H, 1), dtype=torch.float32, device=v.device)], dim=-1)
         qf, kf = q.float(), k.float()
         if inv_freq is not None:
             qf, kf = self._turn_halves(qf, positions.long(), inv_freq), self._turn_halves(kf, positions.long(), inv_freq)
@@ -92,25 +207,40 @@ class TorchOps:
             z = decay_logits.float()
             if decay_bias is not None:
                 z = z + decay_bias.float().reshape(1, H, D)
-            a = torch.exp(torch.nn.functional.logsigmoid(z) / tau)
+            a = torch.exp(-torch.exp(z)) if decay_mode == "exp_neg_exp" else torch.exp(torch.nn.functional.logsigmoid(z) / tau)
+        elif token_decay is not None:
+            a = token_decay.float().reshape(T, H, 1).expand(T, H, D)
         else:
             a = head_decay.float().reshape(1, H, 1).expand(T, H, D)
+        if token_k_scale is not None:
+            kf = kf * token_k_scale.float().reshape(T, H, 1)
+        u = bonus.float().reshape(H, D) if bonus is not None else None
         out = torch.empty((T, H, Dv), dtype=torch.float32, device=q.device)
         for b in range(num_seqs):
             slot = int(state_slots[b])
             S = state[slot].clone()
             for t in range(int(cu_seqlens[b]), int(cu_seqlens[b + 1])):
-                S = a[t][:, :, None] * S + kf[t][:, :, None] * v[t].float()[:, None, :]
-                out[t] = torch.einsum("hdv,hd->hv", S, qf[t])
+                kv = kf[t][:, :, None] * vf[t][:, None, :]
+                if u is not None:  # the present token counts with the bonus, the state is read before its update
+                    out[t] = torch.einsum("hdv,hd->hv", S + u[:, :, None] * kv, qf[t])
+                S = a[t][:, :, None] * S + kv
+                if u is None:
+                    out[t] = torch.einsum("hdv,hd->hv", S, qf[t])
             state[slot] = S
         return out
 
-    def head_norm_gate(self, o, gate, out, *, weight, eps, out_scale=1.0):
+    def head_norm_gate(self, o, gate, out, *, weight, eps, out_scale=1.0, gate_act="silu", per_head_weight=False,
+                       denominator=None):
+        T, H, Dv = out.shape
+        if denominator is not None:  # o's last column is n . q; the value columns are divided first
+            den = torch.maximum(o[:, :, Dv].abs(), torch.exp(-denominator.float())) + 1e-6
+            o = o[:, :, :Dv] / den[:, :, None]
         x = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
         if weight is not None:
-            x = x * weight.float()
+            x = x * (weight.float().reshape(H, Dv) if per_head_weight else weight.float())
         g = gate.float()
-        out.copy_((x * (g / (1 + torch.exp(-g))) * out_scale).to(out.dtype))
+        act = torch.sigmoid(g) if gate_act == "sigmoid" else g / (1 + torch.exp(-g))
+        out.copy_((x * act * out_scale).to(out.dtype))
         return out
 
     def conv_rope_store(self, x, *, num_heads, num_kv_heads, head_dim, value_dim, conv_weight, conv_state, inv_freq,
@@ -191,7 +321,7 @@ class TorchOps:
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
                         token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None,
-                        value_dim=None):
+                        value_dim=None, keep_first=0, sink=None, gate=None):
         T = out.shape[0]
         D = head_dim
         group = num_heads // num_kv_heads
@@ -199,7 +329,7 @@ class TorchOps:
             p = int(positions[t])
             lo = max(0, p - window + 1) if window else 0
             table = block_table[int(token_seq[t])]
-            js = torch.arange(lo, p + 1)
+            js = torch.cat([torch.arange(0, min(keep_first, lo)), torch.arange(lo, p + 1)])
             pages = table[(js // page_size).to(table.device)].long()
             offs = (js % page_size).to(pages.device)
             keys = k_pages[pages, :, offs, :].float()  # [n, nkv, D]
@@ -208,8 +338,15 @@ class TorchOps:
             kh = keys.repeat_interleave(group, dim=1)  # [n, nq, D]
             vh = vals.repeat_interleave(group, dim=1)
             scores = torch.einsum("hd,nhd->hn", qt, kh) * scale
-            probs = torch.softmax(scores, dim=-1)
-            out[t] = torch.einsum("hn,nhd->hd", probs, vh).reshape(-1).to(out.dtype)
+            if sink is not None:  # one more score that has no value
+                scores = torch.cat([scores, torch.full((num_heads, 1), float(sink), device=scores.device)], dim=-1)
+                probs = torch.softmax(scores, dim=-1)[:, :-1]
+            else:
+                probs = torch.softmax(scores, dim=-1)
+            res = torch.einsum("hn,nhd->hd", probs, vh).reshape(-1)
+            if gate is not None:
+                res = res * torch.sigmoid(gate[t].float())
+            out[t] = res.to(out.dtype)
         return out
 
     # ---- attention through a latent ------------------------------------------------------
@@ -270,7 +407,22 @@ class TorchOps:
         return out
 
     # ---- routed experts ----------------------------------------------------------------
-    def route_top(self, h, router, top, renormalize=False, score="sigmoid"):
+    def route_top(self, h, router, top, renormalize=False, score="sigmoid", correction=None, groups=None):
+        if score == "softmax_all":
+            s_all = torch.softmax(h.float() @ router.float().t(), dim=-1)
+            choice = s_all + correction.float() if correction is not None else s_all.clone()
+            if groups and groups[0] > 1:
+                count, keep = groups
+                E = choice.shape[1]
+                best = choice.reshape(-1, count, E // count).max(-1).values
+                kept = torch.zeros_like(best, dtype=torch.bool)
+                kept.scatter_(1, best.topk(keep, dim=-1).indices, True)
+                choice = choice.masked_fill(~kept.repeat_interleave(E // count, dim=1), float("-inf"))
+            chosen = choice.topk(top, dim=-1).indices
+            w = s_all.gather(1, chosen)
+            if renormalize:
+                w = w / (w.sum(-1, keepdim=True) + 1e-20)
+            return chosen.to(torch.int32), w.float()
         best = torch.topk(h.float() @ router.float().t(), top, dim=-1)  # on the logits: no saturated ties
         if score == "softmax_chosen":
             return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1).float()
@@ -287,13 +439,16 @@ class TorchOps:
         return out
 
     def routed_experts(self, h, chosen, weights, gate_up, down, *, limit=0.0, alpha=1.0, up_offset=0.0,
-                       weight_on="input", shared=None, activation="clamped_glu", shared_gate=None):
+                       weight_on="input", shared=None, activation="clamped_glu", shared_gate=None, num_identity=0):
         T, W = h.shape
         gated = activation == "clamped_glu"
         F = gate_up.shape[1] // 2 if gated else gate_up.shape[1]
         total = torch.zeros((T, W), dtype=torch.float32, device=h.device)
         for t in range(T):
             for e, w in zip(chosen[t].tolist(), weights[t].tolist()):
+                if e >= gate_up.shape[0]:  # an identity expert: the input itself, times the weight
+                    total[t] += h[t].float() * w
+                    continue
                 x = (h[t].float() * w).to(h.dtype) if weight_on == "input" else h[t]
                 gu = (gate_up[e].float() @ x.float()).to(h.dtype)
                 mid = torch.empty((1, F), dtype=h.dtype, device=h.device)
