@@ -1,7 +1,11 @@
 // Causal attention over the paged cache for any mix of prompt portions and single
 // decoded tokens: the general kernel (any head_dim up to 256 (multiples of 8 with
 // 16-byte loads), a value size of its own up to 256, any head counts, any page size, optional
-// window), used by the fp32 path and wherever a specialised kernel refuses a size.
+// window), used by the fp32 path and wherever a specialised kernel refuses a size.  Options: a
+// window that leaves the sequence's first `keep_first` keys readable (they are visited first, in
+// tiles of their own, then the window's); a sink, one more score without a value in the softmax's
+// denominator, p_j = exp(s_j) / (exp(sink) + sum exp(s_j')); a gate, the result times
+// sigmoid(gate[t, h, d]) before the one rounding.
 //
 // One warp per (token, query head).  The query at absolute position p attends to
 // keys lo..p of its own sequence (lo = p - window + 1 with a window, else 0), which
@@ -20,7 +24,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
                                                const int* __restrict__ token_seq,
                                                const int* __restrict__ positions, T* __restrict__ out,
                                                long out_stride, int num_tokens, int nq, int nkv, int D, int Dv, int ps, float scale,
-                                               int window) {
+                                               int window, int keep_first, int has_sink, float sink,
+                                               const T* __restrict__ gate, long gate_stride) {
   extern __shared__ float qs_all[];  // WARPS * D
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long item = (long)blockIdx.x * WARPS + warp;
@@ -39,69 +44,88 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
   float acc[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-  for (int j0 = lo & ~31; j0 <= p; j0 += 32) {
-    const int j = j0 + lane;
-    const bool valid = j >= lo && j <= p;
-    long row = 0;  // the key's row among all (page, head, place) rows; keys have D, values Dv elements
-    float s = -INFINITY;
-    if (valid) {
-      const int page = bt[j / ps];
-      row = ((long)page * nkv + kvh) * ps + (j % ps);
-      const T* kr = kpages + row * D;
-      float dot = 0.f;
-      if ((D & 7) == 0) {
-        for (int d = 0; d < D; d += 8) {
-          float kv[8];
-          load8(kr + d, kv);
+  // keys first..last (inclusive) of this range; tiles start at multiples of 32
+  const int kept_last = min(keep_first, lo) - 1;  // the kept first keys that the window does not hold
+  for (int range = kept_last >= 0 ? 0 : 1; range < 2; ++range) {
+    const int first = range ? lo : 0, last = range ? p : kept_last;
+    for (int j0 = first & ~31; j0 <= last; j0 += 32) {
+      const int j = j0 + lane;
+      const bool valid = j >= first && j <= last;
+      long row = 0;  // the key's row among all (page, head, place) rows; keys have D, values Dv elements
+      float s = -INFINITY;
+      if (valid) {
+        const int page = bt[j / ps];
+        row = ((long)page * nkv + kvh) * ps + (j % ps);
+        const T* kr = kpages + row * D;
+        float dot = 0.f;
+        if ((D & 7) == 0) {
+          for (int d = 0; d < D; d += 8) {
+            float kv[8];
+            load8(kr + d, kv);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+            for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+          }
+        } else {  // rows that are not 16-byte multiples: one element at a time
+          for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
         }
-      } else {  // rows that are not 16-byte multiples: one element at a time
-        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
+        s = dot * scale;
       }
-      s = dot * scale;
-    }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float pl = valid ? expf(s - m_new) : 0.f;
-    const float corr = expf(m - m_new);
-    l = l * corr + warp_sum(pl);
+      const float m_new = fmaxf(m, warp_max(s));
+      const float pl = valid ? expf(s - m_new) : 0.f;
+      const float corr = expf(m - m_new);
+      l = l * corr + warp_sum(pl);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] *= corr;
-    const int count = min(32, p - j0 + 1);
-    for (int jj = 0; jj < count; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, pl, jj);
-      const long rj = __shfl_sync(0xffffffffu, row, jj);
-      if (pj == 0.f) continue;  // keys before the window, or fully underflowed
-      const T* vr = vpages + rj * Dv;
+      for (int c = 0; c < 8; ++c) acc[c] *= corr;
+      const int count = min(32, last - j0 + 1);
+      for (int jj = 0; jj < count; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, pl, jj);
+        const long rj = __shfl_sync(0xffffffffu, row, jj);
+        if (pj == 0.f) continue;  // keys before the window, or fully underflowed
+        const T* vr = vpages + rj * Dv;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int d = lane + 32 * c;
-        if (d < Dv) acc[c] = fmaf(pj, to_f32(vr[d]), acc[c]);
+        for (int c = 0; c < 8; ++c) {
+          const int d = lane + 32 * c;
+          if (d < Dv) acc[c] = fmaf(pj, to_f32(vr[d]), acc[c]);
+        }
       }
+      m = m_new;
     }
-    m = m_new;
   }
   T* orow = out + (long)t * out_stride + (long)h * Dv;
+  if (has_sink) {  // one more score in the denominator
+    const float m_all = fmaxf(m, sink), corr = expf(m - m_all);
+    l = l * corr + expf(sink - m_all);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] *= corr;
+  }
   const float inv = 1.f / l;
+  const T* grow = gate ? gate + (long)t * gate_stride + (long)h * Dv : nullptr;
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     const int d = lane + 32 * c;
-    if (d < Dv) orow[d] = from_f32<T>(acc[c] * inv);
+    if (d < Dv) {
+      float val = acc[c] * inv;
+      if (grow) val *= 1.f / (1.f + expf(-to_f32(grow[d])));
+      orow[d] = from_f32<T>(val);
+    }
   }
 }
 
 // q: [num_tokens, *] with row stride q_stride (elements), head h at column h*D.  Keys are
 // [pages, nkv, ps, D], values [pages, nkv, ps, Dv].  out: rows out_stride elements apart, head h at
-// column h*Dv.  window <= 0: none.
+// column h*Dv.  window <= 0: none; keep_first counts only with a window; gate: rows gate_stride elements
+// apart, head h at column h*Dv, or null.
 Q3_EXPORT int q3_paged_attention_generic(int dtype, const void* q, int q_stride, const void* kpages,
                                          const void* vpages, const int* block_table, int max_pages,
                                          const int* token_seq, const int* positions, void* out,
                                          long out_stride, int num_tokens, int nq, int nkv, int D, int Dv, int ps,
-                                         float scale,
-                                         int window, cudaStream_t stream) {
+                                         float scale, int window, int keep_first, int has_sink, float sink,
+                                         const void* gate, long gate_stride, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !token_seq || !positions || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1) return Q3_ERR_ARGUMENT;
   if (D < 1 || D > 256 || Dv < 1 || Dv > 256 || out_stride < (long)nq * Dv) return Q3_ERR_UNSUPPORTED;
+  if (keep_first < 0 || (gate && gate_stride < (long)nq * Dv)) return Q3_ERR_ARGUMENT;
+  if (window <= 0) keep_first = 0;
   if (num_tokens == 0) return Q3_OK;
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * D * sizeof(float);
@@ -110,11 +134,13 @@ Q3_EXPORT int q3_paged_attention_generic(int dtype, const void* q, int q_stride,
   if (dtype == Q3_DTYPE_F32)
     paged_attention_generic_kernel<float, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
         (const float*)q, q_stride, (const float*)kpages, (const float*)vpages, block_table, max_pages,
-        token_seq, positions, (float*)out, out_stride, num_tokens, nq, nkv, D, Dv, ps, scale, window);
+        token_seq, positions, (float*)out, out_stride, num_tokens, nq, nkv, D, Dv, ps, scale, window, keep_first,
+        has_sink, sink, (const float*)gate, gate_stride);
   else if (dtype == Q3_DTYPE_BF16)
     paged_attention_generic_kernel<bf16, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table, max_pages,
-        token_seq, positions, (bf16*)out, out_stride, num_tokens, nq, nkv, D, Dv, ps, scale, window);
+        token_seq, positions, (bf16*)out, out_stride, num_tokens, nq, nkv, D, Dv, ps, scale, window, keep_first,
+        has_sink, sink, (const bf16*)gate, gate_stride);
   else
     return Q3_ERR_ARGUMENT;
   return q3_launch_status();

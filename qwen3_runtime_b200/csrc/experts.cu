@@ -124,11 +124,91 @@ __global__ void route_pick_kernel(float* __restrict__ logits, int num_tokens, in
     for (int k = lane; k < top; k += 32) weights[(long)t * top + k] /= total;
 }
 
+// mode 3: s = softmax over all E logits; the choice is made on c = s + correction (correction null: on s)
+// among the outputs of the `keep` best of `count` equal groups of neighbours (a group's score: its largest
+// c; count <= 1: no groups), lowest index on a tie; the weights are the chosen s, divided by their sum +
+// 1e-20 when `renorm`.  One warp per token; c and the groups' scores wait in shared memory.
+__global__ void route_pick_softmax_all_kernel(const float* __restrict__ logits, int num_tokens, int E, int top,
+                                              const float* __restrict__ correction, int count, int keep, int renorm,
+                                              int* __restrict__ chosen, float* __restrict__ weights) {
+  extern __shared__ float pick_smem[];  // per warp: c[E], group scores[count]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= num_tokens) return;
+  const int groups = count > 1 ? count : 0;
+  float* c = pick_smem + (long)warp * (E + groups);
+  float* gs = c + E;
+  const float* z = logits + (long)t * E;
+  float zmax = -INFINITY;
+  for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+  zmax = warp_max(zmax);
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) den += expf(z[e] - zmax);
+  den = warp_sum(den);
+  for (int e = lane; e < E; e += 32) c[e] = expf(z[e] - zmax) / den + (correction ? correction[e] : 0.f);
+  __syncwarp();
+  if (groups) {
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
+      gs[g] = best;
+    }
+    __syncwarp();
+    // a group stays if fewer than `keep` groups come before it (larger score, or equal and lower index)
+    for (int g = lane; g < groups; g += 32) {
+      const float mine = gs[g];
+      int before = 0;
+      for (int o = 0; o < groups; ++o) before += gs[o] > mine || (gs[o] == mine && o < g);
+      if (before >= keep)
+        for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = c[e];
+      if (v > best || (v == best && e < at)) {
+        best = v;
+        at = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) {
+        best = ob;
+        at = oa;
+      }
+    }
+    if (at >= E) at = k;  // nothing left to choose from (more choices than open outputs): never read
+    const float score = expf(z[at] - zmax) / den;
+    if (lane == 0) {
+      chosen[(long)t * top + k] = at;
+      weights[(long)t * top + k] = score;
+      c[at] = NAN;  // taken: compares false with everything
+    }
+    total += score;
+    __syncwarp();
+  }
+  if (renorm)
+    for (int k = lane; k < top; k += 32) weights[(long)t * top + k] /= total + 1e-20f;
+}
+
 // logits: fp32 scratch [num_tokens, E] (left with the chosen entries at -inf).
+// mode 3 takes correction (fp32 [E] or null), count and keep (groups) and renorm; the other modes ignore them.
 Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float* router, int num_tokens, int E, int W,
-                           int top, int mode, float* logits, int* chosen, float* weights,
-                           cudaStream_t stream) {
+                           int top, int mode, float* logits, int* chosen, float* weights, const float* correction,
+                           int count, int keep, int renorm, cudaStream_t stream) {
   if (!h || !router || !logits || !chosen || !weights || E < 1 || W < 1 || top < 1 || top > E) return Q3_ERR_ARGUMENT;
+  if (mode == 3 && count > 1 && (E % count || keep < 1 || keep > count || top > keep * (E / count)))
+    return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
   int tt = ROUTE_TT;  // fewer tokens per block when their rows would not fit in shared memory
   while (tt > 1 && (size_t)tt * W * sizeof(float) > 128 * 1024) tt >>= 1;
@@ -150,6 +230,13 @@ Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float*
     return Q3_ERR_ARGUMENT;
   }
   if (e != cudaSuccess) return Q3_ERR_LAUNCH;
+  if (mode == 3) {
+    const size_t pick = (size_t)4 * (E + (count > 1 ? count : 0)) * sizeof(float);
+    if (pick > 48 * 1024) return Q3_ERR_UNSUPPORTED;
+    e = launch_pdl(route_pick_softmax_all_kernel, dim3((num_tokens + 3) / 4), dim3(128), pick, stream,
+                   (const float*)logits, num_tokens, E, top, correction, count, keep, renorm, chosen, weights);
+    return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+  }
   e = launch_pdl(route_pick_kernel, dim3((num_tokens + 3) / 4), dim3(128), 0, stream, logits, num_tokens, E, top,
                  mode, chosen, weights);
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
@@ -650,7 +737,8 @@ Q3_EXPORT int q3_expert_up_tc(const void* h, long h_stride, const void* up, void
 template <typename T>
 __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict__ weights, const T* __restrict__ shared,
                                const T* __restrict__ shared_gate, long gate_stride, T* __restrict__ out, long total,
-                               int W, int top) {
+                               int W, int top, const int* __restrict__ chosen, int stored, const T* __restrict__ h,
+                               long h_stride) {
   pdl_wait();
   pdl_launch_dependents();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -659,7 +747,9 @@ __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict_
   const int i = (int)(idx - t * W);
   float sum = 0.f;
   for (int k = 0; k < top; ++k) {
-    const float v = to_f32(y[(t * top + k) * W + i]);
+    // a choice beyond the stored experts stands for an expert that returns its input
+    const bool same = chosen && chosen[t * top + k] >= stored;
+    const float v = same ? to_f32(h[t * h_stride + i]) : to_f32(y[(t * top + k) * W + i]);
     sum += weights ? v * weights[t * top + k] : v;
   }
   if (shared) {
@@ -671,21 +761,25 @@ __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict_
 
 // y: [T * top, W]; weights: fp32 [T * top] or null (the weight was applied to the input);
 // shared: [T, W] or null; shared_gate: one logit per token, gate_stride elements apart, or null: the
-// shared expert's result is multiplied by the logit's sigmoid; out: [T, W].
+// shared expert's result is multiplied by the logit's sigmoid; out: [T, W].  chosen (int32 [T * top], with
+// h [T, W] rows h_stride apart, or null): a slot whose choice is >= `stored` takes the token's row of h in
+// place of y.
 Q3_EXPORT int q3_expert_combine(int dtype, const void* y, const float* weights, const void* shared,
                                 const void* shared_gate, long gate_stride, void* out, int num_tokens, int W, int top,
-                                cudaStream_t stream) {
-  if (!y || !out || W < 1 || top < 1) return Q3_ERR_ARGUMENT;
+                                const int* chosen, int stored, const void* h, long h_stride, cudaStream_t stream) {
+  if (!y || !out || W < 1 || top < 1 || (chosen && !h)) return Q3_ERR_ARGUMENT;
   const long total = (long)num_tokens * W;
   if (total == 0) return Q3_OK;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32)
     e = launch_pdl(combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)y, weights,
-                   (const float*)shared, (const float*)shared_gate, gate_stride, (float*)out, total, W, top);
+                   (const float*)shared, (const float*)shared_gate, gate_stride, (float*)out, total, W, top, chosen,
+                   stored, (const float*)h, h_stride);
   else if (dtype == Q3_DTYPE_BF16)
     e = launch_pdl(combine_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)y, weights,
-                   (const bf16*)shared, (const bf16*)shared_gate, gate_stride, (bf16*)out, total, W, top);
+                   (const bf16*)shared, (const bf16*)shared_gate, gate_stride, (bf16*)out, total, W, top, chosen,
+                   stored, (const bf16*)h, h_stride);
   else
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;

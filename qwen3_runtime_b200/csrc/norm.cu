@@ -656,3 +656,117 @@ Q3_EXPORT int q3_relu_squared(int dtype, const void* x, long x_stride, void* out
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
+
+// ---- grouped RMSNorm of a sum with up to two pending outputs and up to two weights ------------------
+//   add = (planes summed in order | pending) + more          v = resid[r] + add        (fp32)
+//   resid[r] = v                                              (when write_resid)
+//   a row is cut into `groups` equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps):
+//   out[i] = unit(v) * w        out2[i] = unit(v) * w2        (w null: out[i] = v rounded, nothing normalised)
+// One block per row; the values wait in shared memory, the groups' mean squares are taken by whole
+// warps in turn (a fixed tree per group), so a row's bits do not depend on the rows around it.
+template <typename T>
+__global__ void grouped_norm_kernel(const void* __restrict__ pending, int parts, long part_stride,
+                                    const T* __restrict__ more, float* __restrict__ resid,
+                                    const int* __restrict__ rows, const float* __restrict__ w,
+                                    const float* __restrict__ w2, T* __restrict__ out, long out_stride,
+                                    T* __restrict__ out2, int H, int groups, float eps, int write_resid) {
+  extern __shared__ float gvals[];  // H values, then one reciprocal root per group
+  float* rstd = gvals + H;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const long src = rows ? rows[r] : r;
+  const T* prow = pending && !parts ? static_cast<const T*>(pending) + src * H : nullptr;
+  const float* frow = pending && parts ? static_cast<const float*>(pending) + src * H : nullptr;
+  const T* mrow = more ? more + src * H : nullptr;
+  float* rrow = resid + src * H;
+  T* orow = out + (long)r * out_stride;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float add = 0.f;
+    bool any = false;
+    if (frow) {
+      add = frow[i];
+      for (int p = 1; p < parts; ++p) add += frow[p * part_stride + i];
+      any = true;
+    } else if (prow) {
+      add = to_f32(prow[i]);
+      any = true;
+    }
+    if (mrow) add = any ? add + to_f32(mrow[i]) : to_f32(mrow[i]);
+    const float v = (any || mrow) ? rrow[i] + add : rrow[i];
+    if (write_resid) rrow[i] = v;
+    if (w) gvals[i] = v; else orow[i] = from_f32<T>(v);
+  }
+  if (!w) return;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const int Hg = H / groups;
+  for (int g = warp; g < groups; g += nwarp) {
+    float ss = 0.f;
+    for (int i = lane; i < Hg; i += 32) {
+      const float v = gvals[g * Hg + i];
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) rstd[g] = rsqrtf(ss / (float)Hg + eps);
+  }
+  __syncthreads();
+  T* orow2 = out2 ? out2 + (long)r * H : nullptr;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float u = gvals[i] * rstd[i / Hg];
+    orow[i] = from_f32<T>(u * w[i]);
+    if (orow2) orow2[i] = from_f32<T>(u * w2[i]);
+  }
+}
+
+// pending: `dtype` [*, H] when pending_parts is 0, else fp32 planes part_stride elements apart (or null);
+// more: `dtype` [*, H] or null; resid fp32 [*, H]; out rows out_stride elements apart; out2 dense or null
+// (needs w2); w null: out gets the sum itself.
+Q3_EXPORT int q3_grouped_norm(int dtype, const void* pending, int pending_parts, long part_stride, const void* more,
+                              float* resid, const int* rows, const float* w, const float* w2, void* out,
+                              long out_stride, void* out2, int num_rows, int H, int groups, float eps,
+                              int write_resid, cudaStream_t stream) {
+  if (!resid || !out || H < 1 || groups < 1 || H % groups || out_stride < H) return Q3_ERR_ARGUMENT;
+  if ((out2 && !w2) || (w2 && !w) || pending_parts < 0 || (pending_parts && !pending)) return Q3_ERR_ARGUMENT;
+  if (num_rows == 0) return Q3_OK;
+  const size_t smem = (size_t)(H + groups) * sizeof(float);
+  if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(grouped_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(grouped_norm_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, pending, pending_parts,
+                   part_stride, (const float*)more, resid, rows, w, w2, (float*)out, out_stride, (float*)out2, H, groups,
+                   eps, write_resid);
+  } else if (dtype == Q3_DTYPE_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(grouped_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(grouped_norm_kernel<bf16>, dim3(num_rows), dim3(threads), smem, stream, pending, pending_parts,
+                   part_stride, (const bf16*)more, resid, rows, w, w2, (bf16*)out, out_stride, (bf16*)out2, H, groups,
+                   eps, write_resid);
+  } else {
+    return Q3_ERR_ARGUMENT;
+  }
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// ---- tanh in place ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void tanh_rows_kernel(T* __restrict__ x, long total) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = from_f32<T>(tanhf(to_f32(x[i])));
+}
+
+Q3_EXPORT int q3_tanh_rows(int dtype, void* x, long total, cudaStream_t stream) {
+  if (!x || total < 0) return Q3_ERR_ARGUMENT;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32) e = launch_pdl(tanh_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, total);
+  else if (dtype == Q3_DTYPE_BF16) e = launch_pdl(tanh_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, total);
+  else return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}

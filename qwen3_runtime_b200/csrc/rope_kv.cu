@@ -244,3 +244,81 @@ Q3_EXPORT int q3_rope_table(const float* inv_freq, float* cos_t, float* sin_t, i
   rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, cos_t, sin_t, max_pos, half);
   return q3_launch_status();
 }
+
+// ---- per-head q/k RMSNorm and cache write without a rotation, for rows whose k and v blocks start at
+// columns of their own and whose values have a size of their own ------------------------------------
+// One warp per (token, head).  q heads (columns h * D) are normalised in place; k heads (columns
+// k_start + g * D) are normalised into their page rows; v heads (columns v_start + g * Dv) are copied.
+// Key pages [pages, nkv, ps, D], value pages [pages, nkv, ps, Dv].  A weight of null leaves q (or k) as
+// it is.
+template <typename T, int WARPS>
+__global__ void qk_norm_store_kernel(T* __restrict__ proj, long row_stride, int nq, int nkv, int D, int Dv,
+                                     int k_start, int v_start, const float* __restrict__ q_w,
+                                     const float* __restrict__ k_w, float eps, const int* __restrict__ positions,
+                                     const int* __restrict__ token_seq, const int* __restrict__ block_table,
+                                     int max_pages, T* __restrict__ kpages, T* __restrict__ vpages, int ps,
+                                     int num_tokens, int write_kv) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = write_kv ? nq + 2 * nkv : nq;
+  const long item = (long)blockIdx.x * WARPS + warp;
+  if (item >= (long)num_tokens * heads) return;
+  const int t = (int)(item / heads);
+  const int hi = (int)(item - (long)t * heads);
+  T* row = proj + (long)t * row_stride;
+  const int p = positions[t];
+  long slot = 0;  // the token's row among all (page, head, place) rows
+  if (hi >= nq) {
+    const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
+    if (p < 0 || p / ps >= max_pages) return;  // no page in the table for this position: write nothing
+    const int page = block_table[(long)token_seq[t] * max_pages + p / ps];
+    if (page < 0) return;
+    slot = ((long)page * nkv + kvh) * ps + (p % ps);
+  }
+  if (hi >= nq + nkv) {  // value head: plain copy
+    const T* x = row + v_start + (long)(hi - nq - nkv) * Dv;
+    T* dst = vpages + slot * Dv;
+    for (int d = lane; d < Dv; d += 32) dst[d] = x[d];
+    return;
+  }
+  T* x = hi < nq ? row + (long)hi * D : row + k_start + (long)(hi - nq) * D;
+  T* dst = hi < nq ? x : kpages + slot * D;
+  const float* w = hi < nq ? q_w : k_w;
+  if (!w) {
+    if (dst != x)
+      for (int d = lane; d < D; d += 32) dst[d] = x[d];
+    return;
+  }
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = to_f32(x[d]);
+    ss += v * v;
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / (float)D + eps);
+  for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>((to_f32(x[d]) * rstd) * w[d]);
+}
+
+Q3_EXPORT int q3_qk_norm_store(int dtype, void* proj, long row_stride, int nq, int nkv, int D, int Dv, int k_start,
+                               int v_start, const float* q_w, const float* k_w, float eps, const int* positions,
+                               const int* token_seq, const int* block_table, int max_pages, void* kpages,
+                               void* vpages, int ps, int num_tokens, int write_kv, cudaStream_t stream) {
+  if (!proj || !positions || nq < 1 || nkv < 1 || D < 1 || Dv < 1 || ps < 1) return Q3_ERR_ARGUMENT;
+  if (write_kv && (!token_seq || !block_table || !kpages || !vpages || max_pages < 1)) return Q3_ERR_ARGUMENT;
+  if (num_tokens == 0) return Q3_OK;
+  constexpr int WARPS = 4;
+  const long items = (long)num_tokens * (write_kv ? nq + 2 * nkv : nq);
+  const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(qk_norm_store_kernel<float, WARPS>, dim3(blocks), dim3(WARPS * 32), 0, stream, (float*)proj,
+                   row_stride, nq, nkv, D, Dv, k_start, v_start, q_w, k_w, eps, positions, token_seq, block_table,
+                   max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(qk_norm_store_kernel<bf16, WARPS>, dim3(blocks), dim3(WARPS * 32), 0, stream, (bf16*)proj,
+                   row_stride, nq, nkv, D, Dv, k_start, v_start, q_w, k_w, eps, positions, token_seq, block_table,
+                   max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}

@@ -61,6 +61,16 @@ _SIGNATURES = {
                               c_void_p],
         "q3_relu_squared": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "q3_clamped_glu": [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p],
+        "q3_grouped_norm": [c_int, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_long, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "q3_tanh_rows": [c_int, c_void_p, c_long, c_void_p],
+    },
+    "token_state": {
+        "q3_bigram_embed": [c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_long, c_long, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                            c_void_p],
+        "q3_token_shift_mix": [c_int, c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "latent_attention": {
         "q3_latent_norm_rope_store": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
@@ -83,7 +93,7 @@ _SIGNATURES = {
     },
     "experts": {
         "q3_route_top": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                         c_void_p, c_void_p],
+                         c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "q3_group_slots": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "q3_expert_gate_up_tc": [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p],
@@ -94,7 +104,7 @@ _SIGNATURES = {
         "q3_expert_down": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],
         "q3_expert_combine": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_int, c_int, c_int,
-                              c_void_p],
+                              c_void_p, c_int, c_void_p, c_long, c_void_p],
         "q3_expert_up": [c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                          c_void_p, c_void_p, c_int, c_void_p],
         "q3_expert_up_tc": [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -105,18 +115,24 @@ _SIGNATURES = {
                                   c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "q3_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "q3_qk_norm_store": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                             c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_void_p],
     },
     "attention_generic": {
         "q3_paged_attention_generic": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                       c_int, c_void_p],
+                                       c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p],
     },
     "linear_state": {
         "q3_decayed_state_scan": [c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long,
                                   c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p,
-                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "q3_head_norm_gate": [c_int, c_void_p, c_void_p, c_float, c_void_p, c_long, c_void_p, c_long, c_float, c_int,
-                              c_int, c_int, c_void_p],
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_int, c_void_p, c_void_p],
+        "q3_head_norm_gate": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_long, c_void_p, c_long,
+                              c_float, c_int, c_int, c_int, c_int, c_void_p],
+        "q3_stabilised_gates": [c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
     "short_conv": {
         "q3_conv_rope_store": [c_int, c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -353,6 +369,96 @@ class CudaOps:
                   _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab)
         return out
 
+    def grouped_norm(self, out, weight, eps, groups, *, resid, pending=None, pending_more=None, rows=None,
+                     write_resid=True, num_rows=None, out2=None, weight2=None):
+        """RMSNorm in ``groups`` equal consecutive parts of ``resid + pending + pending_more`` (each part divided
+        by its own root mean square, the weight spanning the row), float32 throughout; see csrc/norm.cu.
+        ``pending``: ``[rows, H]`` of the output's type or fp32 partial sums ``[parts, rows, H]``;
+        ``pending_more``: ``[rows, H]`` of the output's type.  ``out2`` / ``weight2``: a second normalised copy
+        of the same rows with another weight.  ``weight=None``: ``out`` (rows may be views of wider rows) gets
+        the sum itself, rounded."""
+        H = resid.shape[-1]
+        n = out.shape[0] if num_rows is None else num_rows
+        if resid.dtype != torch.float32 or not resid.is_contiguous() or out.shape[-1] != H or out.stride(-1) != 1:
+            raise KernelError("grouped_norm: a dense float32 residual sum and output rows of its width")
+        parts = stride = 0
+        if pending is not None and pending.dim() == 3:
+            if pending.dtype != torch.float32 or pending.stride(2) != 1 or pending.stride(1) != H:
+                raise KernelError("grouped_norm: partial sums are fp32 [parts, rows, H] with dense rows")
+            parts, stride = pending.shape[0], pending.stride(0)
+        elif pending is not None and (pending.dtype != out.dtype or not pending.is_contiguous()):
+            raise KernelError("grouped_norm: a pending output is dense [rows, H] of the output's type")
+        if pending_more is not None and (pending_more.dtype != out.dtype or not pending_more.is_contiguous()):
+            raise KernelError("grouped_norm: a second pending output is dense [rows, H] of the output's type")
+        if out2 is not None and (weight2 is None or weight is None or not out2.is_contiguous()
+                                 or out2.dtype != out.dtype):
+            raise KernelError("grouped_norm: a second output is dense, of the first one's type, with a weight of its own")
+        for w in (weight, weight2):
+            if w is not None and (w.dtype != torch.float32 or w.numel() != H or not w.is_contiguous()):
+                raise KernelError("grouped_norm: weights are dense float32 vectors of the rows' width")
+        if self.timing is not None:
+            e = out.element_size()
+            self._costs(n * H * (4 + (4 if write_resid else 0) + e * (1 + (out2 is not None))
+                                 + (4 * parts if parts else (e if pending is not None else 0))
+                                 + (e if pending_more is not None else 0)))
+        self._call("norm", "q3_grouped_norm", "grouped_norm", _dtype_code(out.dtype), _ptr(pending), parts, stride,
+                   _ptr(pending_more), _ptr(resid), _ptr(rows), _ptr(weight), _ptr(weight2), _ptr(out), out.stride(0),
+                   _ptr(out2), n, H, int(groups), float(eps), int(bool(write_resid)))
+        return out
+
+    def tanh_rows(self, x):
+        """``x = tanh(x)`` in place (float32 math, one rounding)."""
+        if not x.is_contiguous():
+            raise KernelError("tanh_rows: a dense tensor")
+        self._call("norm", "q3_tanh_rows", "tanh_rows", _dtype_code(x.dtype), _ptr(x), x.numel())
+        return x
+
+    # ---- what a layer keeps of a sequence's previous token (csrc/token_state.cu) -----------------
+    def bigram_embed(self, ids, *, embed, scale, bigram, buckets, mul_prev, mul_cur, prev_state, positions,
+                     token_seq, cu_seqlens, state_slots, num_seqs, out, copy=None):
+        """``out[t] = embed[id_t] * scale + bigram[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]`` (float32
+        rows; row ``buckets`` for a sequence's first token); the token before a step's first comes from
+        ``prev_state`` (int32 ``[slots, 1]``), which then takes the step's last token.  ``copy``: the same rows
+        in the tables' type (may be a view of wider rows).  ``bigram=None``: the scaled lookup alone."""
+        T, W = out.shape
+        if out.dtype != torch.float32 or not out.is_contiguous() or not embed.is_contiguous() or embed.shape[1] != W:
+            raise KernelError("bigram_embed: dense float32 output rows of the table's width")
+        if bigram is not None and (bigram.dtype != embed.dtype or bigram.shape != (buckets + 1, W)
+                                   or not bigram.is_contiguous() or prev_state is None
+                                   or prev_state.dtype != torch.int32 or not prev_state.is_contiguous()):
+            raise KernelError("bigram_embed: a dense bigram table [buckets + 1, width] of the embedding's type and "
+                              "an int32 slot per request")
+        if copy is not None and (copy.dtype != embed.dtype or copy.stride(1) != 1 or copy.shape != (T, W)):
+            raise KernelError("bigram_embed: the copy has the tables' type and unit-stride rows")
+        if self.timing is not None:
+            e = embed.element_size()
+            self._costs(T * W * (4 + e * (1 + (bigram is not None) + (copy is not None))))
+        self.launches += int(bigram is not None)  # the slot's update is a kernel of its own
+        self._call("token_state", "q3_bigram_embed", "bigram_embed", _dtype_code(embed.dtype), _ptr(ids), _ptr(embed),
+                   float(scale), _ptr(bigram), int(buckets), int(mul_prev), int(mul_cur), _ptr(prev_state),
+                   _ptr(positions), _ptr(token_seq), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out), _ptr(copy),
+                   copy.stride(0) if copy is not None else 0, T, int(num_seqs), W, embed.shape[0])
+        return out
+
+    def token_shift_mix(self, h, mu, *, state, positions, token_seq, cu_seqlens, state_slots, num_seqs):
+        """``y[s, t] = h[t] + (h[t-1] - h[t]) * mu[s]`` for each row s of ``mu`` (float32 ``[n, W]``), h[-1] = 0
+        for a sequence's first token; the row before a step's first comes from ``state`` (float32
+        ``[slots, W]``), which then takes the step's last row.  Returns ``[n, T, W]`` of h's type."""
+        T, W = h.shape
+        n = mu.shape[0]
+        if h.stride(1) != 1 or mu.dtype != torch.float32 or not mu.is_contiguous() or mu.shape[1] != W:
+            raise KernelError("token_shift_mix: unit-stride rows and dense float32 blends [n, width]")
+        if state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1:] != (W,):
+            raise KernelError("token_shift_mix: the state is dense float32 [slots, width]")
+        out = torch.empty((n, T, W), dtype=h.dtype, device=h.device)
+        if self.timing is not None:
+            self._costs(T * W * h.element_size() * (n + 1))
+        self.launches += 1  # the slot's update is a kernel of its own
+        self._call("token_state", "q3_token_shift_mix", "token_shift_mix", _dtype_code(h.dtype), _ptr(h), h.stride(0),
+                   _ptr(mu), n, _ptr(state), _ptr(positions), _ptr(token_seq), _ptr(cu_seqlens), _ptr(state_slots),
+                   _ptr(out), T, int(num_seqs), W)
+        return out
+
     def add_bias(self, out, bias):
         """``out[r] += bias`` in place (``bias`` float32): the bias of a projection."""
         N = out.shape[-1]
@@ -415,15 +521,30 @@ class CudaOps:
     # ---- decayed matrix state (csrc/linear_state.cu) and short convolution (csrc/short_conv.cu) ----
     def decayed_state_scan(self, q, k, v, *, state, cu_seqlens, state_slots, num_seqs, decay_logits=None,
                            decay_bias=None, tau=1.0, head_decay=None, inv_freq=None, positions=None, q_scale=1.0,
-                           k_scale=1.0):
+                           k_scale=1.0, decay_mode="sigmoid_pow", token_decay=None, token_k_scale=None, bonus=None,
+                           ones_column=False):
         """``S_t = diag(a_t) S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` per (sequence, head) on the float32
         state ``[slots, H, D, Dv]`` of the sequences' slots; returns float32 ``o`` ``[T, H, Dv]``.
         ``q, k`` ``[T, H, D]``, ``v`` ``[T, H, Dv]`` (views of wider rows allowed).  The decay is
         ``sigmoid(decay_logits + decay_bias)^(1 / tau)`` per key channel, or ``head_decay`` (float32
         ``[H]``) per head.  ``inv_freq`` (float32 ``[pairs]``): q and k are rotated first (pair i =
-        elements i and i + pairs); then multiplied by ``q_scale`` / ``k_scale``."""
+        elements i and i + pairs); then multiplied by ``q_scale`` / ``k_scale``.
+        ``decay_mode="exp_neg_exp"``: the decay is ``exp(-exp(decay_logits + decay_bias))``.  ``token_decay`` /
+        ``token_k_scale`` (float32 ``[T, H]``): a decay per (token, head) in place of ``head_decay``, and a
+        factor on k.  ``ones_column``: the values get one more column whose value is 1 (state and ``o`` then
+        have ``Dv + 1`` columns; the last one of ``o`` is q times the decayed sum of the keys).  ``bonus``
+        (float32 ``[H * D]``): ``o_t = (S_(t-1) + diag(bonus) k_t v_t^T)^T q_t``, the state read before its
+        update."""
         T, H, D = q.shape
-        Dv = v.shape[2]
+        Dv = v.shape[2] + int(bool(ones_column))
+        modes = {"sigmoid_pow": 0, "exp_neg_exp": 1}
+        if decay_mode not in modes:
+            raise KernelError(f"decayed_state_scan: unknown decay mode {decay_mode!r}")
+        for x, what in ((token_decay, "token_decay"), (token_k_scale, "token_k_scale")):
+            if x is not None and (x.dtype != torch.float32 or x.shape != (T, H) or not x.is_contiguous()):
+                raise KernelError(f"decayed_state_scan: {what} is dense float32 [tokens, heads]")
+        if bonus is not None and (bonus.dtype != torch.float32 or bonus.numel() != H * D or not bonus.is_contiguous()):
+            raise KernelError("decayed_state_scan: the bonus is dense float32 [heads * dim]")
         for x, what in ((q, "q"), (k, "k"), (v, "v")):
             if x.stride(2) != 1 or x.stride(1) != x.shape[2]:
                 raise KernelError(f"decayed_state_scan: the heads of {what} lie side by side in a row")
@@ -442,23 +563,55 @@ class CudaOps:
                    q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
                    _ptr(decay_bias), 1.0 / float(tau), _ptr(head_decay), _ptr(inv_freq), pairs, _ptr(positions),
                    float(q_scale), float(k_scale), _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out),
-                   int(num_seqs), H, D, Dv)
+                   int(num_seqs), H, D, Dv, modes[decay_mode], _ptr(token_decay), _ptr(token_k_scale),
+                   int(bool(ones_column)), _ptr(bonus))
         return out
 
-    def head_norm_gate(self, o, gate, out, *, weight, eps, out_scale=1.0):
-        """``out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) * out_scale``:
+    def stabilised_gates(self, zi, zf, *, i_bias, f_bias, cap, m_state, cu_seqlens, state_slots, num_seqs):
+        """The gates of a matrix memory with exponential gates and a running maximum m per (sequence, head)
+        (float32 ``[slots, H]``, updated): ``li = cap tanh((zi + bi) / cap)``, ``lf = logsigmoid(cap tanh((zf +
+        bf) / cap))``, ``m_t = max(lf + m_(t-1), li)``; returns float32 ``[T, H]`` ``decay = exp(lf + m_(t-1) -
+        m_t)``, ``k_scale = exp(li - m_t)`` and ``m_t``.  ``zi``, ``zf``: ``[T, H]`` views of rows of one width."""
+        T, H = zi.shape
+        if zi.stride(1) != 1 or zf.stride(1) != 1 or zi.stride(0) != zf.stride(0) or zf.shape != zi.shape:
+            raise KernelError("stabilised_gates: the two gates are [tokens, heads] views of rows of one width")
+        if m_state.dtype != torch.float32 or not m_state.is_contiguous() or m_state.shape[1:] != (H,):
+            raise KernelError("stabilised_gates: the running maximum is dense float32 [slots, heads]")
+        for b in (i_bias, f_bias):
+            if b is not None and (b.dtype != torch.float32 or b.numel() != H or not b.is_contiguous()):
+                raise KernelError("stabilised_gates: biases are dense float32 [heads]")
+        decay = torch.empty((3, T, H), dtype=torch.float32, device=zi.device)
+        self._call("linear_state", "q3_stabilised_gates", "stabilised_gates", _dtype_code(zi.dtype), _ptr(zi), _ptr(zf),
+                   zi.stride(0), _ptr(i_bias), _ptr(f_bias), float(cap), _ptr(m_state), _ptr(cu_seqlens),
+                   _ptr(state_slots), _ptr(decay[0]), _ptr(decay[1]), _ptr(decay[2]), int(num_seqs), H)
+        return decay[0], decay[1], decay[2]
+
+    def head_norm_gate(self, o, gate, out, *, weight, eps, out_scale=1.0, gate_act="silu", per_head_weight=False,
+                       denominator=None):
+        """``out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]) * out_scale``:
         ``o`` float32 ``[T, H, Dv]``, ``gate`` and ``out`` ``[T, H, Dv]`` views of rows, ``weight``
-        float32 ``[Dv]`` or None."""
-        T, H, Dv = o.shape
+        float32 ``[Dv]`` (``per_head_weight``: ``[H * Dv]``) or None, ``gate_act`` ``"silu"`` or ``"sigmoid"``.
+        ``denominator`` (float32 ``[T, H]``, a running maximum m): ``o`` has one more column c, and its values are
+        first divided by ``max(|c|, exp(-m)) + 1e-6``."""
+        T, H, Dv = out.shape
+        acts = {"silu": 0, "sigmoid": 1}
+        if gate_act not in acts:
+            raise KernelError(f"head_norm_gate: unknown gate activation {gate_act!r}")
         for x in (gate, out):
-            if x.shape != o.shape or x.stride(2) != 1 or x.stride(1) != Dv:
+            if x.shape != (T, H, Dv) or x.stride(2) != 1 or x.stride(1) != Dv:
                 raise KernelError("head_norm_gate: gate and output are [T, H, Dv] with the heads side by side")
-        if o.dtype != torch.float32 or not o.is_contiguous():
-            raise KernelError("head_norm_gate: o is dense float32")
+        if o.dtype != torch.float32 or not o.is_contiguous() or o.shape != (T, H, Dv + (denominator is not None)):
+            raise KernelError("head_norm_gate: o is dense float32 [T, H, Dv] (one more column with a denominator)")
+        if denominator is not None and (denominator.dtype != torch.float32 or denominator.shape != (T, H)
+                                        or not denominator.is_contiguous()):
+            raise KernelError("head_norm_gate: the denominator's maximum is dense float32 [T, H]")
+        if weight is not None and weight.numel() != (H * Dv if per_head_weight else Dv):
+            raise KernelError("head_norm_gate: the weight spans one head's values, or all heads' (per_head_weight)")
         if self.timing is not None:
             self._costs(T * H * Dv * (4 + 2 * out.element_size()))
-        self._call("linear_state", "q3_head_norm_gate", "head_norm_gate", _dtype_code(out.dtype), _ptr(o), _ptr(weight),
-                   float(eps), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), float(out_scale), T, H, Dv)
+        self._call("linear_state", "q3_head_norm_gate", "head_norm_gate", _dtype_code(out.dtype), _ptr(o),
+                   _ptr(denominator), _ptr(weight), int(bool(per_head_weight)), float(eps), _ptr(gate), gate.stride(0),
+                   _ptr(out), out.stride(0), float(out_scale), acts[gate_act], T, H, Dv)
         return out
 
     def conv_rope_store(self, x, *, num_heads, num_kv_heads, head_dim, value_dim, conv_weight, conv_state, inv_freq,
@@ -606,17 +759,28 @@ class CudaOps:
         return out
 
     # ---- routed experts (csrc/experts.cu) --------------------------------------------------------
-    def route_top(self, h, router, top, renormalize=False, score="sigmoid"):
+    def route_top(self, h, router, top, renormalize=False, score="sigmoid", correction=None, groups=None):
         """``(chosen int32 [T, top], weights float32 [T, top])``: the float32 router product, the
         ``top`` largest per token in descending order (chosen on the logits, which order the experts as
         their sigmoids do without the ties of a saturated sigmoid; lowest index on an exact tie).
         ``score="sigmoid"``: the weights are the chosen logits' sigmoids (``renormalize``: divided by
-        their sum); ``"softmax_chosen"``: the softmax over the chosen logits only."""
-        if score not in ("sigmoid", "softmax_chosen"):
+        their sum); ``"softmax_chosen"``: the softmax over the chosen logits only; ``"softmax_all"``: s is
+        the softmax over all outputs, the choice is made on ``s + correction`` (float32 ``[E]`` or None) among
+        the outputs of the ``groups[1]`` best of ``groups[0]`` equal groups of neighbours (a group's score: its
+        largest choice score), and the weights are the chosen s (``renormalize``: over their sum + 1e-20)."""
+        if score not in ("sigmoid", "softmax_chosen", "softmax_all"):
             raise KernelError(f"route_top: unknown score {score!r}")
-        mode = 2 if score == "softmax_chosen" else int(bool(renormalize))
+        mode = 3 if score == "softmax_all" else (2 if score == "softmax_chosen" else int(bool(renormalize)))
         T, W = h.shape
         E = router.shape[0]
+        count, keep = (int(groups[0]), int(groups[1])) if groups else (0, 0)
+        if mode != 3 and (correction is not None or groups):
+            raise KernelError("route_top: a correction and groups go with score='softmax_all'")
+        if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E
+                                       or not correction.is_contiguous()):
+            raise KernelError("route_top: the correction is a dense float32 vector, one number per router output")
+        if count > 1 and (E % count or not 1 <= keep <= count or top > keep * (E // count)):
+            raise KernelError(f"route_top: {E} outputs in {count} groups of which {keep} stay cannot give {top} choices")
         if router.dtype != torch.float32 or not router.is_contiguous() or router.shape[1] != W or h.stride(1) != 1:
             raise KernelError("route_top: a dense float32 router [experts, width]")
         chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
@@ -626,18 +790,24 @@ class CudaOps:
             self._costs(E * W * 4 + T * W * h.element_size(), 2.0 * T * E * W)
         self.launches += 1  # two kernels: the logits, then the choice
         self._call("experts", "q3_route_top", "route_top", _dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(router),
-                   T, E, W, top, mode, _ptr(logits), _ptr(chosen), _ptr(weights))
+                   T, E, W, top, mode, _ptr(logits), _ptr(chosen), _ptr(weights), _ptr(correction), count, keep,
+                   int(bool(renormalize)))
         return chosen, weights
 
     def routed_experts(self, h, chosen, weights, gate_up, down, *, limit=0.0, alpha=1.0, up_offset=0.0,
-                       weight_on="input", shared=None, activation="clamped_glu", shared_gate=None):
+                       weight_on="input", shared=None, activation="clamped_glu", shared_gate=None, num_identity=0):
         """Every token through its chosen experts: ``gate_up`` ``[E, 2F, W]`` (gate rows, then up
         rows), ``down`` ``[E, W, F]``; the slots are grouped by expert on the device, each expert's two
         products run over its slots only, and a token's results (and ``shared`` ``[T, W]``) are summed
         in float32.  ``activation="relu2"``: the experts have no gate, ``gate_up`` is the up weight
         ``[E, F, W]`` and the unit is the squared ReLU (the weight then multiplies the output).
-        ``shared_gate`` ``[T]`` (a view of one column will do): ``shared`` is multiplied by its sigmoid."""
+        ``shared_gate`` ``[T]`` (a view of one column will do): ``shared`` is multiplied by its sigmoid.
+        ``num_identity``: choices ``E .. E + num_identity - 1`` stand for experts that return their input; their
+        slots run through no product and the token's own row is summed with the slot's weight."""
         T, W = h.shape
+        num_identity = int(num_identity)
+        if num_identity and weight_on != "output":
+            raise KernelError("routed_experts: identity experts take their weight on the output")
         gated = activation == "clamped_glu"
         if activation not in ("clamped_glu", "relu2"):
             raise KernelError(f"routed_experts: unknown activation {activation!r}")
@@ -653,14 +823,17 @@ class CudaOps:
             raise KernelError("routed_experts: experts without a gate take their weight on the output")
         if shared_gate is not None and (shared is None or shared_gate.shape != (T,) or shared_gate.dtype != h.dtype):
             raise KernelError("routed_experts: one gate logit per token, of the activations' type")
-        plan = torch.empty(2 * (E + 1) + S, dtype=torch.int32, device=dev)
-        offsets, tile_offsets, order = plan[: E + 1], plan[E + 1: 2 * (E + 1)], plan[2 * (E + 1):]
+        # identity experts are grouped like the stored ones (behind them); the products then stop at the stored
+        # experts' last tile
+        EA = E + num_identity
+        plan = torch.empty(2 * (EA + 1) + S, dtype=torch.int32, device=dev)
+        offsets, tile_offsets, order = plan[: EA + 1], plan[EA + 1: 2 * (EA + 1)], plan[2 * (EA + 1):]
         # bfloat16 with 16-byte rows: the products run on the tensor cores, in row tiles of 64 slots when
         # an expert gets about that many, else of 32
         tensor_cores = (self.experts_tc and h.dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0
                         and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
         bm = 64 if tensor_cores and S >= 48 * E else 32
-        self._call("experts", "q3_group_slots", "group_slots", _ptr(chosen), S, E, bm, _ptr(offsets),
+        self._call("experts", "q3_group_slots", "group_slots", _ptr(chosen), S, EA, bm, _ptr(offsets),
                    _ptr(tile_offsets), _ptr(order))
         mid = torch.empty((S, F), dtype=h.dtype, device=dev)
         y = torch.empty((S, W), dtype=h.dtype, device=dev)
@@ -697,7 +870,8 @@ class CudaOps:
             self._costs((S + T + (T if shared is not None else 0)) * W * e)
         self._call("experts", "q3_expert_combine", "expert_combine", code, _ptr(y),
                    None if on_input else _ptr(weights), _ptr(shared), _ptr(shared_gate),
-                   shared_gate.stride(0) if shared_gate is not None else 0, _ptr(out), T, W, top)
+                   shared_gate.stride(0) if shared_gate is not None else 0, _ptr(out), T, W, top,
+                   _ptr(chosen) if num_identity else None, E, _ptr(h) if num_identity else None, h.stride(0))
         return out
 
     # ---- position encoding + cache write -----------------------------------------------
@@ -734,18 +908,41 @@ class CudaOps:
                   _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages),
                   page_size, T, int(bool(write_kv)), self.PAIRINGS[pairing], _ptr(self._error_word(qkv.device)))
 
+    def qk_norm_store(self, proj, *, num_heads, num_kv_heads, head_dim, value_dim, k_start, v_start, q_weight,
+                      k_weight, eps, positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+        """Per-head q/k RMSNorm (weights float32 ``[head_dim]`` shared by the heads, or None: as they are) without
+        a rotation, and the write of k and v into their pages (csrc/rope_kv.cu).  A row of ``proj`` holds the
+        query heads from column 0, the key heads from ``k_start`` and the value heads (``value_dim`` each) from
+        ``v_start``; q is normalised in place."""
+        T = proj.shape[0]
+        if proj.stride(1) != 1:
+            raise KernelError("qk_norm_store: unit-stride rows")
+        max_pages = block_table.shape[1] if block_table is not None else 0
+        if self.timing is not None:
+            self._costs(2 * T * ((num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim) * proj.element_size())
+        self._call("rope_kv", "q3_qk_norm_store", "qk_norm_store", _dtype_code(proj.dtype), _ptr(proj), proj.stride(0),
+                   num_heads, num_kv_heads, head_dim, value_dim, int(k_start), int(v_start), _ptr(q_weight),
+                   _ptr(k_weight), float(eps), _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages,
+                   _ptr(k_pages), _ptr(v_pages), page_size, T, int(bool(write_kv)))
+
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
                         token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None,
-                        value_dim=None):
+                        value_dim=None, keep_first=0, sink=None, gate=None):
         """Causal attention of every token of the step over its sequence's pages.  ``value_dim``:
         values have a size of their own (``v_pages`` ``[pages, kv heads, page, value_dim]``); ``out`` may
-        then be a view of wider rows, head h at column ``h * value_dim``."""
+        then be a view of wider rows, head h at column ``h * value_dim``.  ``keep_first``: with a window, the
+        sequence's first tokens stay visible as well.  ``sink``: a score without a value that is added to the
+        softmax's denominator.  ``gate`` ``[T, heads * value_dim]`` (a view of wider rows will do): the result
+        is multiplied by its sigmoid."""
         T = out.shape[0]
         if head_dim > 256:
             raise KernelError(f"paged_attention: head_dim={head_dim} is not supported (sizes up to 256 are)")
         Dv = int(value_dim or head_dim)
-        dense = out.stride(0) == num_heads * Dv and Dv == head_dim
+        plain = not (window and keep_first) and sink is None and gate is None  # what the specialised kernels take
+        dense = out.stride(0) == num_heads * Dv and Dv == head_dim and plain
+        if gate is not None and (gate.stride(1) != 1 or gate.shape != (T, num_heads * Dv) or gate.dtype != out.dtype):
+            raise KernelError("paged_attention: the gate is [tokens, heads * value_dim] of the output's type")
         if Dv > 256 or out.stride(1) != 1:
             raise KernelError(f"paged_attention: value_dim={Dv} is not supported (up to 256, unit stride)")
         if (dense and step is not None and step.decode_only and out.dtype == torch.bfloat16 and head_dim in (64, 128, 256)
@@ -808,7 +1005,8 @@ class CudaOps:
         self._call("attention_generic", "q3_paged_attention_generic", "paged_attention",
                    _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                   block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads,
-                  num_kv_heads, head_dim, Dv, page_size, float(scale), int(window or 0))
+                  num_kv_heads, head_dim, Dv, page_size, float(scale), int(window or 0), int(keep_first or 0),
+                  int(sink is not None), float(sink or 0.0), _ptr(gate), gate.stride(0) if gate is not None else 0)
         return out
 
     @staticmethod
