@@ -46,6 +46,10 @@ kinds and a roofline fraction per kind):
 * ``puladra``      the same comparison for the Puladra design (gated linear attention, windowed
                    attention with a short convolution beside retention, routed squared-ReLU experts,
                    a per-layer token input) at two layer sizes;
+* ``medilix``      the Medilix design (matrix memories with stabilised exponential gates and with token
+                   shift, a bonus and per-channel decays; attention with a sink, a window that keeps the first
+                   tokens and an output gate; grouped routing with identity experts; two grouped norms per
+                   layer) at two layer sizes beside the Puladra design at equal sizes, its closest relative;
 * ``decode``, ``latency``, ``batch8``, ``throughput``, ``prefill``, ``longctx``: the six closed
                    batches of the reference's own harness (bench/workloads.py:34-43) at Qwen3-4B
                    sizes, with its token budget rule (bench/workloads.py:52-64).
@@ -96,7 +100,7 @@ BASELINE_TOK_S = 693.26
 # (concurrency = requests, prompt tokens, output tokens) of the reference's closed batches
 CLOSED_CASES = {"decode": (1, 256, 512), "latency": (1, 512, 128), "batch8": (8, 256, 128),
                 "throughput": (16, 256, 128), "prefill": (1, 2048, 16), "longctx": (1, 8192, 64)}
-WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", "puladra", *CLOSED_CASES)
+WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", "puladra", "medilix", *CLOSED_CASES)
 
 # Layer sizes for the Puladra design that resemble real models of its kinds of layer: gated linear
 # attention with keys of half and values of the full width, windowed attention with grouped key/value
@@ -112,6 +116,21 @@ PULADRA_SIZES = {
                   left=dict(heads=32, kv_heads=8, dim=128, vdim=128, conv=4, window=2048),
                   right=dict(heads=16, dim=64, vdim=128), experts=32, top=4, expert_ff=2048, shared_ff=2048,
                   side=256, layers=4, vocab=32000),
+}
+
+# Layer sizes for the Medilix design: matrix memories with keys of 64 and values of 128 (mlstm) or keys and
+# values of 64 (wkv, twice the heads), attention with grouped key/value heads of 128, a window and 64 kept
+# first tokens, routed SiLU experts in 8 groups of which 4 are kept, 8 identity experts among the router's
+# outputs, the last layer with a clamped dense feed-forward of the routed layers' active width.  Four layers
+# (mlstm, attention, wkv, attention), no loop; beside each the Puladra design with the same widths, heads,
+# state sizes, window, expert count and active feed-forward width (no shared expert, no token input).
+MEDILIX_SIZES = {
+    "w2048": dict(width=2048, heads=16, mem=dict(heads=16, dim=64, vdim=128), wkv=dict(heads=32, dim=64, rank=64),
+                  att=dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=64),
+                  experts=56, identity=8, top=6, expert_ff=1408, groups=(8, 4), norm_groups=4, layers=4, vocab=32000),
+    "w4096": dict(width=4096, heads=32, mem=dict(heads=32, dim=64, vdim=128), wkv=dict(heads=64, dim=64, rank=64),
+                  att=dict(heads=32, kv_heads=8, dim=128, vdim=128, window=2048, keep=64),
+                  experts=28, identity=4, top=4, expert_ff=2048, groups=(8, 4), norm_groups=4, layers=4, vocab=32000),
 }
 
 # Layer sizes for the Logesun design (attention through a latent with a window and a sink, routed
@@ -637,6 +656,40 @@ def _puladra_config(z: dict):
                          side_dim=z["side"])
 
 
+def _medilix_config(z: dict):
+    from qwen3_runtime_b200.config import MedilixConfig
+    from qwen3_runtime_b200.config.medilix_config import (BigramConfig, DenseConfig, GatedAttentionConfig,
+                                                          MedilixLayerConfig, MlstmConfig, MoeConfig, WkvConfig)
+
+    m, w, a = z["mem"], z["wkv"], z["att"]
+    moe = MoeConfig(experts=z["experts"], identity=z["identity"], top=z["top"], ff=z["expert_ff"],
+                    groups=z["groups"][0], groups_keep=z["groups"][1])
+    att = GatedAttentionConfig(heads=a["heads"], kv_heads=a["kv_heads"], dim=a["dim"], vdim=a["vdim"],
+                               scale=a["dim"] ** -0.5, window=a["window"], keep_first=a["keep"])
+    layers = (MedilixLayerConfig("mlstm", MlstmConfig(heads=m["heads"], dim=m["dim"], vdim=m["vdim"], gate_cap=15.0), moe),
+              MedilixLayerConfig("attention", att, moe),
+              MedilixLayerConfig("wkv", WkvConfig(heads=w["heads"], dim=w["dim"], decay_rank=w["rank"]), moe),
+              MedilixLayerConfig("attention", att, DenseConfig(ff=z["top"] * z["expert_ff"], limit=7.0)))
+    return MedilixConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, norm_groups=z["norm_groups"],
+                         embed_scale=1.0, bigram=BigramConfig(buckets=65521, mul_prev=40503, mul_cur=1), layers=layers)
+
+
+def _puladra_twin_config(z: dict):
+    """Puladra at the sizes of a Medilix entry: its gated linear attention has the mlstm's heads and sizes, its
+    windowed attention the attention's, its retention the wkv's."""
+    m, w, a = z["mem"], z["wkv"], z["att"]
+    return _puladra_config(dict(
+        vocab=z["vocab"], width=z["width"], layers=z["layers"], side=0, experts=z["experts"] + z["identity"],
+        top=z["top"], expert_ff=z["expert_ff"], shared_ff=0, gla=dict(heads=m["heads"], dim=m["dim"], vdim=m["vdim"], rank=16),
+        left=dict(heads=a["heads"], kv_heads=a["kv_heads"], dim=a["dim"], vdim=a["vdim"], conv=4, window=a["window"]),
+        right=dict(heads=w["heads"] // 2, dim=w["dim"], vdim=2 * w["dim"])))
+
+
+def run_medilix(args, pk) -> dict:
+    return run_design_beside_dense(args, pk, "medilix", "Medilix", MEDILIX_SIZES, _medilix_config,
+                                   twin=("puladra", _puladra_twin_config, "the Puladra design"))
+
+
 def run_logesun(args, pk) -> dict:
     return run_design_beside_dense(args, pk, "logesun", "Logesun", LOGESUN_SIZES, _logesun_config)
 
@@ -650,11 +703,14 @@ def _fill_cache(storage) -> None:
     finite numbers."""
     for t in storage.tensors:
         for x in (t if isinstance(t, tuple) else (t,)):
-            x.normal_(0.0, 0.5)
+            if x.is_floating_point():  # integer rows (a previous token id) stay zero
+                x.normal_(0.0, 0.5)
 
 
-def run_design_beside_dense(args, pk, workload: str, design: str, sizes: dict, make_config) -> dict:
-    """Prefill and decode of a design beside a Qwen3 dense model of equal size."""
+def run_design_beside_dense(args, pk, workload: str, design: str, sizes: dict, make_config,
+                            twin=("qwen3_dense", _dense_twin_config, "a Qwen3 dense model")) -> dict:
+    """Prefill and decode of a design beside another model of equal size: ``twin`` = (its label in the results,
+    its configuration for an entry of ``sizes``, its name in the metric's text)."""
     import torch
 
     from qwen3_runtime_b200.engine.factory import build_model, build_runtime
@@ -668,7 +724,7 @@ def run_design_beside_dense(args, pk, workload: str, design: str, sizes: dict, m
     clocks = ClockSampler().start()
     results = {}
     for size, z in sizes.items():
-        for arm, cfg in ((workload, make_config(z)), ("qwen3_dense", _dense_twin_config(z))):
+        for arm, cfg in ((workload, make_config(z)), (twin[0], twin[1](z))):
             ops = CudaOps()
             model = build_model(cfg, RandomDeviceSource(expected_tensors_for(cfg), SEED, "cuda"), dtype="bfloat16",
                                 ops=ops)
@@ -689,8 +745,8 @@ def run_design_beside_dense(args, pk, workload: str, design: str, sizes: dict, m
             torch.cuda.empty_cache()
     first = results[f"w2048/{workload}"]
     return {
-        "metric": f"decode tok/s @ batch 8, ctx 1024 ({design} w2048 sizes, 4 layers, bf16); beside it a Qwen3 dense "
-                  "model of equal size, and one 2048-token prefill of each",
+        "metric": f"decode tok/s @ batch 8, ctx 1024 ({design} w2048 sizes, 4 layers, bf16); beside it {twin[2]} "
+                  "of equal size, and one 2048-token prefill of each",
         "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "impl": "ours", "workload": workload,
@@ -713,6 +769,8 @@ def run_workload_ours(args) -> dict:
         return run_logesun(args, pk)
     if args.workload == "puladra":
         return run_puladra(args, pk)
+    if args.workload == "medilix":
+        return run_medilix(args, pk)
     cases = workload_prompts(args.workload, np)
     results, cfg, build_s, engine = {}, None, 0.0, None
     clocks = ClockSampler()
@@ -970,7 +1028,7 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.workload == "default":
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
-    elif args.workload in ("logesun", "puladra") and args.impl == "reference":
+    elif args.workload in ("logesun", "puladra", "medilix") and args.impl == "reference":
         result = {"impl": "reference", "workload": args.workload,
                   "unavailable": "the reference has no model of this design (it serves Qwen3 dense only)"}
     else:

@@ -50,17 +50,11 @@ def embedding(cfg: dict, w: dict, tokens: list[int]) -> torch.Tensor:
     return x
 
 
-def mlstm_mixer(h, p, w, prefix, eps, dtype):
-    """Matrix memory with exponential gates and a running maximum as stabiliser (starting at 0)."""
-    T = h.shape[0]
-    H, D, Dv, cap = int(p["heads"]), int(p["dim"]), int(p["vdim"]), float(p["gate_cap"])
-    q = lin(h, w[prefix + "q"], dtype).reshape(T, H, D) * D ** -0.5
-    k = lin(h, w[prefix + "k"], dtype).reshape(T, H, D)
-    v = lin(h, w[prefix + "v"], dtype).reshape(T, H, Dv)
-    zi = lin(h, w[prefix + "i"], dtype) + w[prefix + "i.b"].float()
-    zf = lin(h, w[prefix + "f"], dtype) + w[prefix + "f.b"].float()
-    li = cap * torch.tanh(zi / cap)
-    lf = F.logsigmoid(cap * torch.tanh(zf / cap))
+def stabilised_memory(q, k, v, li, lf):
+    """``q, k`` [T, H, D], ``v`` [T, H, Dv], log gates ``li, lf`` [T, H]: the matrix memory S, the sum of keys n
+    and the running maximum m (all from zero), read after the update and divided by max(|n . q|, exp(-m)) + 1e-6."""
+    T, H, D = q.shape
+    Dv = v.shape[2]
     S = torch.zeros(H, D, Dv)
     n = torch.zeros(H, D)
     m = torch.zeros(H)
@@ -75,6 +69,56 @@ def mlstm_mixer(h, p, w, prefix, eps, dtype):
         num = torch.einsum("hdv,hd->hv", S, q[t])
         den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-m)) + 1e-6
         out[t] = num / den[:, None]
+    return out
+
+
+def sink_window_attention(q, k, v, scale, window, keep, sink=True):
+    """``q`` [T, H, D], ``k`` [T, G, D], ``v`` [T, G, Dv]: token i sees j <= i with i - j < window or j < keep
+    (``window`` None: every j <= i); the softmax's denominator has one added (``sink`` False: a plain softmax)."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2])
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    seen = j <= i
+    if window:
+        seen = seen & ((i - j < int(window)) | (j < int(keep)))
+    for hd in range(H):
+        g = hd // (H // G)
+        s = (q[:, hd] @ k[:, g].t()) * scale
+        s = s.masked_fill(~seen, float("-inf"))
+        top = torch.clamp(s.max(-1, keepdim=True).values, min=0.0)
+        e = torch.exp(s - top)
+        prob = e / ((torch.exp(-top) if sink else 0.0) + e.sum(-1, keepdim=True))
+        out[:, hd] = prob @ v[:, g]
+    return out
+
+
+def bonus_memory(r, k, v, decay, u):
+    """``r, k, decay`` [T, H, D], ``v`` [T, H, Dv], ``u`` [H, D]: the state is read before its update, the present
+    token counting with the bonus u; then every key channel decays and the token is added."""
+    T, H, D = r.shape
+    S = torch.zeros(H, D, v.shape[2])
+    out = torch.zeros(T, H, v.shape[2])
+    for t in range(T):
+        kv = k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hdv,hd->hv", S + u[:, :, None] * kv, r[t])
+        S = decay[t][:, :, None] * S + kv
+    return out
+
+
+def mlstm_mixer(h, p, w, prefix, eps, dtype):
+    """Matrix memory with exponential gates and a running maximum as stabiliser (starting at 0)."""
+    T = h.shape[0]
+    H, D, Dv, cap = int(p["heads"]), int(p["dim"]), int(p["vdim"]), float(p["gate_cap"])
+    q = lin(h, w[prefix + "q"], dtype).reshape(T, H, D) * D ** -0.5
+    k = lin(h, w[prefix + "k"], dtype).reshape(T, H, D)
+    v = lin(h, w[prefix + "v"], dtype).reshape(T, H, Dv)
+    zi = lin(h, w[prefix + "i"], dtype) + w[prefix + "i.b"].float()
+    zf = lin(h, w[prefix + "f"], dtype) + w[prefix + "f.b"].float()
+    li = cap * torch.tanh(zi / cap)
+    lf = F.logsigmoid(cap * torch.tanh(zf / cap))
+    out = stabilised_memory(q, k, v, li, lf)
     o = head_unit_norm(out, eps).reshape(T, H * Dv) * w[prefix + "norm"].float()
     gate = torch.sigmoid(lin(h, w[prefix + "g"], dtype))
     return lin(o * gate, w[prefix + "o"], dtype)
@@ -92,20 +136,7 @@ def attention_mixer(h, p, w, prefix, eps, dtype):
     v = lin(h, w[prefix + "v"], dtype).reshape(T, G, Dv)
     q = (head_unit_norm(q, eps) * w[prefix + "q.norm"].float()).to(dtype).float()
     k = (head_unit_norm(k, eps) * w[prefix + "k.norm"].float()).to(dtype).float()
-    out = torch.zeros(T, H, Dv)
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
-    seen = j <= i
-    if window:
-        seen = seen & ((i - j < int(window)) | (j < keep))
-    for hd in range(H):
-        g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].t()) * float(p["scale"])
-        s = s.masked_fill(~seen, float("-inf"))
-        top = torch.clamp(s.max(-1, keepdim=True).values, min=0.0)
-        e = torch.exp(s - top)
-        prob = e / (torch.exp(-top) + e.sum(-1, keepdim=True))
-        out[:, hd] = prob @ v[:, g]
+    out = sink_window_attention(q, k, v, float(p["scale"]), window, keep)
     out = out.to(dtype).float().reshape(T, H * Dv)
     gate = torch.sigmoid(lin(h, w[prefix + "g"], dtype))
     return lin(out * gate, w[prefix + "o"], dtype)
@@ -128,12 +159,7 @@ def wkv_mixer(h, p, w, prefix, eps, dtype):
     z = lin(low, w[prefix + "w2"], dtype) + w[prefix + "w0"].float()
     decay = torch.exp(-torch.exp(z)).reshape(T, H, D)
     u = w[prefix + "u"].float().reshape(H, D)
-    S = torch.zeros(H, D, D)
-    out = torch.zeros(T, H, D)
-    for t in range(T):
-        kv = k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hdv,hd->hv", S + u[:, :, None] * kv, r[t])
-        S = decay[t][:, :, None] * S + kv
+    out = bonus_memory(r, k, v, decay, u)
     o = head_unit_norm(out, eps).reshape(T, H * D) * w[prefix + "norm"].float()
     return lin(o * gate, w[prefix + "o"], dtype)
 
