@@ -43,6 +43,22 @@ struct NewToken {
   int pairing;
 };
 
+// What some designs add to the attention.  keep: with a window, the sequence's first `keep` tokens stay
+// visible.  sink_log2: a score (times log2 e) that has no value and joins the softmax's denominator; minus
+// infinity for none.  gate: null, or rows [tokens][gate_stride] whose first heads * D values gate the result
+// by their sigmoid.
+struct Extras {
+  int keep = 0;
+  float sink_log2 = -INFINITY;
+  const bf16* gate = nullptr;
+  int gate_stride = 0;
+};
+
+// The keys a token at position kv_len - 1 sees are numbered consecutively: the window's keys keep their
+// positions, the kept first tokens that lie before the window take the numbers just below it.
+// first_number: the smallest number in use; a number u stands for position u (u >= lo) or u - first_number.
+__device__ __forceinline__ int first_number(int lo, int keep) { return lo - min(keep, lo); }
+
 constexpr int TILE = 64;     // keys per pipeline stage
 constexpr int WARPS = 4;     // each takes 16 keys of a tile
 constexpr int THREADS = WARPS * 32;
@@ -55,12 +71,14 @@ constexpr int THREADS = WARPS * 32;
 // never wrote its partial, which is loaded but not used.
 template <int D>
 __device__ __forceinline__ void merge_row(const float* __restrict__ mid_o, const float* __restrict__ lse,
-                                          int num_splits, bf16* __restrict__ out_row, int first, int step) {
+                                          int num_splits, bf16* __restrict__ out_row, int first, int step,
+                                          float sink_log2, const bf16* __restrict__ gate_row) {
   float mx = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, __ldcg(lse + s));
+  const float sink_w = exp2f(sink_log2 - mx);  // no sink: 2^(-inf) = 0
   for (int d = 4 * first; d < D; d += 4 * step) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    float wsum = 0.f;
+    float wsum = sink_w;
     for (int s0 = 0; s0 < num_splits; s0 += 8) {
       float4 v[8];
       float ls[8];
@@ -80,6 +98,10 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ mid_o, const
           acc[2] += w * v[j].z;
           acc[3] += w * v[j].w;
         }
+    }
+    if (gate_row) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] *= 1.f / (1.f + __expf(-__bfloat162float(gate_row[d + e])));
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] / wsum, acc[1] / wsum);
     __nv_bfloat162 hi = __floats2bfloat162_rn(acc[2] / wsum, acc[3] / wsum);
@@ -110,11 +132,13 @@ __device__ __forceinline__ bool drew_last_ticket(int* ticket, int num_splits) {
 template <int D>
 __device__ __forceinline__ void merge_pair(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
                                            long first_head, int G, int num_splits, int slices,
-                                           bf16* __restrict__ out_rows) {
+                                           bf16* __restrict__ out_rows, float sink_log2 = -INFINITY,
+                                           const bf16* __restrict__ gate_rows = nullptr) {
   constexpr int PER_ROW = D / 4 < 32 ? D / 4 : 32;  // threads on one row, 4 values each
   for (int g = threadIdx.x / PER_ROW; g < G; g += THREADS / PER_ROW)
     merge_row<D>(mid_o + (first_head + g) * num_splits * D, mid_lse + (first_head + g) * num_splits, slices,
-                 out_rows + (long)g * D, threadIdx.x % PER_ROW, PER_ROW);
+                 out_rows + (long)g * D, threadIdx.x % PER_ROW, PER_ROW, sink_log2,
+                 gate_rows ? gate_rows + (long)g * D : nullptr);
 }
 
 // The launch's slice count is made for its longest sequence.  A shorter sequence is cut into fewer
@@ -124,18 +148,18 @@ __device__ __forceinline__ void merge_pair(const float* __restrict__ mid_o, cons
 // length of the launch's longest sequence, which the blocks otherwise work out for themselves.
 __device__ __forceinline__ int slices_of(const int* __restrict__ kv_lens, const int* __restrict__ seq_list,
                                          int num_seqs, int window, int num_splits, int span,
-                                         const int* __restrict__ longest_len) {
+                                         const int* __restrict__ longest_len, int keep = 0) {
   if (num_splits <= 1) return 1;
   int longest = 0;
   if (longest_len) {  // the caller knows the longest sequence of the launch: one load, nothing to agree on
     const int n = *longest_len;
-    const int first = window > 0 ? max(0, n - window) : 0;
+    const int first = first_number(window > 0 ? max(0, n - window) : 0, keep);
     longest = n - (first & ~(TILE - 1));
   } else {
     __shared__ int longest_of_warp[WARPS];
     for (int i = threadIdx.x; i < num_seqs; i += THREADS) {
       const int n = kv_lens[seq_list ? seq_list[i] : i];
-      const int first = window > 0 ? max(0, n - window) : 0;
+      const int first = first_number(window > 0 ? max(0, n - window) : 0, keep);
       longest = max(longest, n - (first & ~(TILE - 1)));
     }
 #pragma unroll
@@ -164,7 +188,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
                         const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
                         float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
                         int num_splits, int stages, NewToken nt, int* __restrict__ error_word,
-                        int* __restrict__ tickets, const int* __restrict__ longest_len) {
+                        int* __restrict__ tickets, const int* __restrict__ longest_len, Extras ex) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -183,9 +207,11 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   const int tok = cu_seqlens[seq];
   const int p = kv_len - 1;
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
-  const int begin0 = lo & ~(TILE - 1);
+  const int lo_n = first_number(lo, ex.keep);  // key numbers lo_n .. lo - 1 are the kept first tokens before the window
+  const int begin0 = lo_n & ~(TILE - 1);
   const int total = kv_len - begin0;
-  const int slices = slices_of(kv_lens, seq_list, gridDim.z, window, num_splits, total, longest_len);
+  const int slices = slices_of(kv_lens, seq_list, gridDim.z, window, num_splits, total, longest_len, ex.keep);
+  const bf16* gate_rows = ex.gate ? ex.gate + (long)tok * ex.gate_stride + (long)kvh * (nq / nkv) * D : nullptr;
   if (split >= slices) return;  // a sequence shorter than the longest: fewer slices, this block has none
   int per = (total + slices - 1) / slices;
   per = (per + TILE - 1) & ~(TILE - 1);
@@ -202,7 +228,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
       pdl_launch_dependents();
       if (drew_last_ticket(ticket, slices))
         merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
-                      out + ((long)tok * nq + kvh * G) * D);
+                      out + ((long)tok * nq + kvh * G) * D, ex.sink_log2, gate_rows);
     }
     return;
   }
@@ -235,26 +261,27 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     const int chunk = tid % CHUNKS;
     for (int r0 = (tid / CHUNKS) * 8; r0 < TILE; r0 += ROWS_PER_PASS) {
       const int j0 = base + r0;
-      if (page_fast) {
+      if (page_fast && j0 >= lo) {  // (key numbers from lo on are positions)
         long src = 0;
-        if (j0 < k_end && j0 + 8 > lo) {
+        if (j0 < k_end) {
           const int page = bt[j0 / ps];
           src = (((long)page * nkv + kvh) * ps + (j0 % ps)) * D + chunk * 8;
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + i;
-          const bool valid = j >= lo && j < k_end && j != skip;
+          const bool valid = j < k_end && j != skip;
           const int off = swz<D>(r0 + i, chunk);
           cp_async16(smem_u32(k_dst + off), kpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
           cp_async16(smem_u32(v_dst + off), vpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
         }
       } else {
         for (int i = 0; i < 8; ++i) {
-          const int j = j0 + i;
-          const bool valid = j >= lo && j < k_end && j != skip;
+          const int u = j0 + i;
+          const bool valid = u >= lo_n && u < k_end && u != skip;
           long src = 0;
           if (valid) {
+            const int j = u >= lo ? u : u - lo_n;
             const int page = bt[j / ps];
             src = (((long)page * nkv + kvh) * ps + (j % ps)) * D + chunk * 8;
           }
@@ -392,7 +419,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int j = key0 + n * 8 + 2 * (lane & 3) + (e & 1);
-        if (j < lo || j >= k_end) s[n][e] = -INFINITY;
+        if (j < lo_n || j >= k_end) s[n][e] = -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
       }
     float corr[2], m_use[2];
@@ -481,17 +508,18 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
       acc += o_s[((size_t)w * 16 + g) * OS + d] * f;
     }
     const int head = kvh * G + g;
-    const float val = acc / l;
     if (slices == 1) {
+      float val = acc / (l + exp2f(ex.sink_log2 - m * scale_log2));
+      if (gate_rows) val *= 1.f / (1.f + __expf(-__bfloat162float(gate_rows[(long)g * D + d])));
       out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(val);
     } else {
-      mid_o[(((long)slot * nq + head) * num_splits + split) * D + d] = val;
+      mid_o[(((long)slot * nq + head) * num_splits + split) * D + d] = acc / l;
       if (d == 0) mid_lse[((long)slot * nq + head) * num_splits + split] = m * scale_log2 + log2f(l);
     }
   }
   if (ticket && drew_last_ticket(ticket, slices))
     merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
-                  out + ((long)tok * nq + kvh * G) * D);
+                  out + ((long)tok * nq + kvh * G) * D, ex.sink_log2, gate_rows);
 }
 
 // The merge as a kernel of its own: one block per (kv head, sequence).
@@ -500,7 +528,7 @@ __global__ void __launch_bounds__(THREADS)
 decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
                       const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                       const int* __restrict__ seq_list, bf16* __restrict__ out, int nq, int nkv, int window,
-                      int num_splits, const int* __restrict__ longest_len) {
+                      int num_splits, const int* __restrict__ longest_len, Extras ex) {
   pdl_wait();
   pdl_launch_dependents();
   const int slot = blockIdx.y, kvh = blockIdx.x;
@@ -508,12 +536,13 @@ decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__
   const int tok = cu_seqlens[seq];
   const int G = nq / nkv;
   const int kv_len = kv_lens[seq];
-  const int lo = window > 0 ? max(0, kv_len - window) : 0;
-  const int slices =
-      slices_of(kv_lens, seq_list, gridDim.y, window, num_splits, kv_len - (lo & ~(TILE - 1)), longest_len);
+  const int lo = first_number(window > 0 ? max(0, kv_len - window) : 0, ex.keep);
+  const int slices = slices_of(kv_lens, seq_list, gridDim.y, window, num_splits, kv_len - (lo & ~(TILE - 1)),
+                               longest_len, ex.keep);
   if (slices == 1) return;  // a sequence in one slice: its block wrote the result itself
   merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
-                out + ((long)tok * nq + kvh * G) * D);
+                out + ((long)tok * nq + kvh * G) * D, ex.sink_log2,
+                ex.gate ? ex.gate + (long)tok * ex.gate_stride + (long)kvh * G * D : nullptr);
 }
 
 template <int D, bool FUSED>
@@ -521,7 +550,7 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
                   int num_splits, const NewToken& nt, int* error_word, int* tickets, const int* longest_len,
-                  cudaStream_t stream) {
+                  const Extras& ex, cudaStream_t stream) {
   const int stages = 2;  // more stages mean fewer blocks per SM; measured equal at best
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
   const size_t merge = (size_t)WARPS * 16 * (D + 8) * 4 + WARPS * 16 * 2 * 4;
@@ -556,14 +585,14 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
     const float scale_log2 = scale * 1.4426950408889634f;
     if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, FUSED>, q, q_stride, kpages, vpages, block_table,
                            max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps, scale_log2,
-                           window, num_splits, stages, nt, error_word, tickets, longest_len) != cudaSuccess)
+                           window, num_splits, stages, nt, error_word, tickets, longest_len, ex) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   if (num_splits > 1 && !tickets) {
     dim3 cgrid(nkv, num_seqs);
     if (launch_pdl(decode_combine_kernel<D>, cgrid, dim3(THREADS), 0, stream, (const float*)mid_o,
                    (const float*)mid_lse, kv_lens, cu_seqlens, seq_list, out, nq, nkv, window, num_splits,
-                   longest_len) != cudaSuccess)
+                   longest_len, ex) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   return Q3_OK;
@@ -574,7 +603,7 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
                     int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, void* out,
                     float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
                     int window, int num_splits, const NewToken& nt, int* error_word, int* tickets,
-                    const int* longest_len, cudaStream_t stream) {
+                    const int* longest_len, cudaStream_t stream, const Extras& ex = Extras{}) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
   if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
@@ -585,7 +614,7 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
     return launch_decode<DIM, FUSED>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages,          \
                                      block_table, max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o,    \
                                      mid_lse, num_seqs, nq, nkv, ps, scale, window, num_splits, nt, error_word,   \
-                                     tickets, longest_len, stream)
+                                     tickets, longest_len, ex, stream)
   switch (D) {
     Q3_DECODE_CASE(64);
     Q3_DECODE_CASE(128);
@@ -619,6 +648,27 @@ Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void*
   return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                 out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
                                 nullptr, tickets, longest_len, stream);
+}
+
+// The same with a window that keeps the sequence's first `keep_first` tokens, a sink (a score without a
+// value in the softmax's denominator; has_sink 0: none) and a gate (null, or rows of gate_stride values of
+// which the first nq * D gate the heads' outputs by their sigmoid; 16-byte alignment is not needed).
+Q3_EXPORT int q3_paged_attention_decode_sink(const void* q, int q_stride, const void* kpages, const void* vpages,
+                                             const int* block_table, int max_pages, const int* kv_lens,
+                                             const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
+                                             float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps,
+                                             float scale, int window, int num_splits, int* tickets,
+                                             const int* longest_len, int keep_first, int has_sink, float sink,
+                                             const void* gate, int gate_stride, cudaStream_t stream) {
+  if (keep_first < 0 || (gate && gate_stride < nq * D)) return Q3_ERR_ARGUMENT;
+  Extras ex;
+  ex.keep = window > 0 ? keep_first : 0;
+  ex.sink_log2 = has_sink ? sink * 1.4426950408889634f : -INFINITY;
+  ex.gate = (const bf16*)gate;
+  ex.gate_stride = gate_stride;
+  return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
+                                out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
+                                nullptr, tickets, longest_len, stream, ex);
 }
 
 // The same, with the work of q3_qk_norm_rope_store folded in: `qkv` is the raw output of the

@@ -10,6 +10,9 @@
 // reference (attention/pytorch.py:45).  The query at absolute position p sees keys
 // max(0, p - window + 1) .. p; p = kv_len - q_len + its index in the portion
 // (attention/pytorch.py:12-15).  Keys the block does not need are zero-filled, never read.
+// Optional: with a window the sequence's first `keep` tokens stay visible (their tiles come before the
+// window's); a sink, a score without a value that joins the softmax's denominator (sink_log2 = score *
+// log2 e, minus infinity for none); a gate whose sigmoid multiplies the result.
 //
 // The block finds its work item by walking cu_seqlens (sequences with one token can be left
 // to the decode kernel: skip_single).
@@ -30,7 +33,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          const bf16* __restrict__ vpages, const int* __restrict__ block_table, int max_pages,
                          const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                          bf16* __restrict__ out, int num_seqs, int nq, int nkv, int ps, float scale_log2,
-                         int window, int skip_single) {
+                         int window, int skip_single, int keep, float sink_log2, const bf16* __restrict__ gate,
+                         int gate_stride) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -87,26 +91,29 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   const int p_min = base_pos + row0 / G, p_max = base_pos + last_row / G;
   const int k_lo = window > 0 ? max(0, p_min - window + 1) : 0;
   const int t_begin = k_lo / TILE, t_end = p_max / TILE;  // inclusive
-  const int num_tiles = t_end - t_begin + 1;
+  // tiles 0 .. kept_tiles - 1 hold kept first tokens that the window's tiles do not
+  const int kept_tiles = min((keep + TILE - 1) / TILE, t_begin);
+  const int num_tiles = kept_tiles + t_end - t_begin + 1;
+  auto tile_key0 = [&](int tile) { return (tile < kept_tiles ? tile : t_begin + tile - kept_tiles) * TILE; };
 
   constexpr int ROWS_PER_PASS = THREADS / CHUNKS * 8;
   const bool page_fast = (ps & 7) == 0;
   auto load_tile = [&](int tile, int stage) {
     unsigned char* k_dst = kv_s + (size_t)stage * 2 * TILE_BYTES;
     unsigned char* v_dst = k_dst + TILE_BYTES;
-    const int base = (t_begin + tile) * TILE;
+    const int base = tile_key0(tile);
     const int chunk = tid % CHUNKS;
     for (int r0 = (tid / CHUNKS) * 8; r0 < TILE; r0 += ROWS_PER_PASS) {
       const int j0 = base + r0;
       long src = 0;
-      if (page_fast && j0 <= p_max && j0 + 8 > k_lo) {
+      if (page_fast && j0 <= p_max && (j0 + 8 > k_lo || j0 < keep)) {
         const int page = bt[j0 / ps];
         src = (((long)page * nkv + kvh) * ps + (j0 % ps)) * D + chunk * 8;
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int j = j0 + i;
-        const bool valid = j >= k_lo && j <= p_max;
+        const bool valid = (j >= k_lo || j < keep) && j <= p_max;
         long s = src + (long)i * D;
         if (!page_fast && valid) {
           const int page = bt[j / ps];
@@ -159,8 +166,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
       if (nxt < num_tiles) load_tile(nxt, nxt % STAGES);
       cp_async_commit();
     }
-    const int key0 = (t_begin + tile) * TILE;
-    if (!warp_live || key0 > wp_max || key0 + TILE - 1 < wlo_min) continue;  // nothing for this warp
+    const int key0 = tile_key0(tile);
+    if (!warp_live || key0 > wp_max || (key0 + TILE - 1 < wlo_min && key0 >= keep)) continue;  // nothing for this warp
     const unsigned char* k_t = kv_s + (size_t)(tile % STAGES) * 2 * TILE_BYTES;
     const unsigned char* v_t = k_t + TILE_BYTES;
 
@@ -185,7 +192,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = key0 + n * 8 + 2 * (lane & 3) + (e & 1);
-          if (j > pos[e >> 1] || j < lo[e >> 1]) s[n][e] = -INFINITY;
+          if (j > pos[e >> 1] || (j < lo[e >> 1] && j >= keep)) s[n][e] = -INFINITY;
         }
     }
     float mx[2] = {-INFINITY, -INFINITY};
@@ -245,8 +252,18 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     const int R = row0 + warp * 16 + (lane >> 2) + r * 8;
     if (R >= rows) continue;
     const int tk = R / G, hd = kvh * G + (R - tk * G);
-    const float inv = 1.f / l_run[r];
+    const float inv = 1.f / (l_run[r] + exp2f(sink_log2 - m_run[r] * scale_log2));  // no sink: 2^(-inf) = 0
     bf16* dst = out + ((long)(tok0 + tk) * nq + hd) * D + 2 * (lane & 3);
+    if (gate) {
+      const bf16* g = gate + (long)(tok0 + tk) * gate_stride + (long)hd * D + 2 * (lane & 3);
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        const float g0 = 1.f / (1.f + __expf(-__bfloat162float(g[i * 8])));
+        const float g1 = 1.f / (1.f + __expf(-__bfloat162float(g[i * 8 + 1])));
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2 * r] * inv * g0, o[i][2 * r + 1] * inv * g1);
+      }
+      continue;
+    }
 #pragma unroll
     for (int i = 0; i < D / 8; ++i)
       *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
@@ -256,7 +273,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 template <int D>
 int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                    int max_pages, const int* kv_lens, const int* cu_seqlens, bf16* out, int num_seqs, int num_work,
-                   int nq, int nkv, int ps, float scale, int window, int skip_single, cudaStream_t stream) {
+                   int nq, int nkv, int ps, float scale, int window, int skip_single, int keep, float sink_log2,
+                   const bf16* gate, int gate_stride, cudaStream_t stream) {
   const size_t smem = (size_t)BLOCK_M * D * 2 + (size_t)STAGES * 2 * TILE * D * 2;
   static bool configured_on[Q3_MAX_DEVICES];
   bool& configured = configured_on[q3_current_device()];
@@ -269,7 +287,8 @@ int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* 
   dim3 grid(num_work, nkv);
   prefill_attention_kernel<D><<<grid, THREADS, smem, stream>>>(q, q_stride, kpages, vpages, block_table, max_pages,
                                                                kv_lens, cu_seqlens, out, num_seqs, nq, nkv, ps,
-                                                               scale * 1.4426950408889634f, window, skip_single);
+                                                               scale * 1.4426950408889634f, window, skip_single,
+                                                               keep, sink_log2, gate, gate_stride);
   return q3_launch_status();
 }
 
@@ -278,22 +297,39 @@ int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* 
 // num_work = sum over the sequences this launch serves of ceil(q_len * (nq / nkv) / 128).
 // head_dim 64 or 128; bfloat16 only.  With skip_single, sequences of one token are left out
 // (their rows of `out` are not written).
+// keep_first: with a window, the sequence's first tokens stay visible.  has_sink / sink: a score without a
+// value in the softmax's denominator.  gate: null, or rows of gate_stride values of which the first nq * D
+// gate the heads' outputs by their sigmoid.
+Q3_EXPORT int q3_paged_attention_prefill_sink(const void* q, int q_stride, const void* kpages, const void* vpages,
+                                              const int* block_table, int max_pages, const int* kv_lens,
+                                              const int* cu_seqlens, void* out, int num_seqs, int num_work, int nq,
+                                              int nkv, int D, int ps, float scale, int window, int skip_single,
+                                              int keep_first, int has_sink, float sink, const void* gate,
+                                              int gate_stride, cudaStream_t stream) {
+  if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
+  if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_seqs < 0 || num_work < 0) return Q3_ERR_ARGUMENT;
+  if (keep_first < 0 || (gate && gate_stride < nq * D)) return Q3_ERR_ARGUMENT;
+  if (q_stride % 8 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
+  if (num_work == 0) return Q3_OK;
+  const int keep = window > 0 ? keep_first : 0;
+  const float sink_log2 = has_sink ? sink * 1.4426950408889634f : -INFINITY;
+  if (D == 64)
+    return launch_prefill<64>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
+                              max_pages, kv_lens, cu_seqlens, (bf16*)out, num_seqs, num_work, nq, nkv, ps, scale,
+                              window, skip_single, keep, sink_log2, (const bf16*)gate, gate_stride, stream);
+  if (D == 128)
+    return launch_prefill<128>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
+                               max_pages, kv_lens, cu_seqlens, (bf16*)out, num_seqs, num_work, nq, nkv, ps, scale,
+                               window, skip_single, keep, sink_log2, (const bf16*)gate, gate_stride, stream);
+  return Q3_ERR_UNSUPPORTED;
+}
+
 Q3_EXPORT int q3_paged_attention_prefill(const void* q, int q_stride, const void* kpages, const void* vpages,
                                          const int* block_table, int max_pages, const int* kv_lens,
                                          const int* cu_seqlens, void* out, int num_seqs, int num_work, int nq,
                                          int nkv, int D, int ps, float scale, int window, int skip_single,
                                          cudaStream_t stream) {
-  if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
-  if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_seqs < 0 || num_work < 0) return Q3_ERR_ARGUMENT;
-  if (q_stride % 8 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
-  if (num_work == 0) return Q3_OK;
-  if (D == 64)
-    return launch_prefill<64>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
-                              max_pages, kv_lens, cu_seqlens, (bf16*)out, num_seqs, num_work, nq, nkv, ps, scale,
-                              window, skip_single, stream);
-  if (D == 128)
-    return launch_prefill<128>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
-                               max_pages, kv_lens, cu_seqlens, (bf16*)out, num_seqs, num_work, nq, nkv, ps, scale,
-                               window, skip_single, stream);
-  return Q3_ERR_UNSUPPORTED;
+  return q3_paged_attention_prefill_sink(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, out,
+                                         num_seqs, num_work, nq, nkv, D, ps, scale, window, skip_single, 0, 0, 0.f,
+                                         nullptr, 0, stream);
 }

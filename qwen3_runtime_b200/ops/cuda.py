@@ -144,6 +144,10 @@ _SIGNATURES = {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "q3_paged_attention_decode_sink": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
+                                           c_int, c_void_p],
         "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
@@ -153,6 +157,9 @@ _SIGNATURES = {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                        c_void_p],
+        "q3_paged_attention_prefill_sink": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                            c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     },
     "attention_prefill_tc": {
         "q3_paged_attention_prefill_tc": [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_long, c_void_p, c_int,
@@ -939,8 +946,10 @@ class CudaOps:
         if head_dim > 256:
             raise KernelError(f"paged_attention: head_dim={head_dim} is not supported (sizes up to 256 are)")
         Dv = int(value_dim or head_dim)
-        plain = not (window and keep_first) and sink is None and gate is None  # what the specialised kernels take
-        dense = out.stride(0) == num_heads * Dv and Dv == head_dim and plain
+        keep_first = int(keep_first or 0) if window else 0
+        plain = not keep_first and sink is None and gate is None  # what the tcgen05 kernel takes
+        dense = out.stride(0) == num_heads * Dv and Dv == head_dim
+        extras = dict(keep_first=keep_first, sink=sink, gate=gate)
         if gate is not None and (gate.stride(1) != 1 or gate.shape != (T, num_heads * Dv) or gate.dtype != out.dtype):
             raise KernelError("paged_attention: the gate is [tokens, heads * value_dim] of the output's type")
         if Dv > 256 or out.stride(1) != 1:
@@ -952,7 +961,7 @@ class CudaOps:
                 v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
                 max_kv_len=step.captured_width * page_size or step.max_kv_len, step=step,
-                num_splits=decode_slices, longest=getattr(step, "kv_longest", None))
+                num_splits=decode_slices, longest=getattr(step, "kv_longest", None), **extras)
         if (dense and step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel
@@ -961,7 +970,7 @@ class CudaOps:
             qlens = [cu[b + 1] - cu[b] for b in range(step.num_seqs)]
             work = sum(-(-n * group // 128) for n in qlens if n > 1)
             done = False
-            if (work and head_dim == 128 and not window and 128 % group == 0 and page_size in (8, 16, 32, 64)
+            if (work and head_dim == 128 and not window and plain and 128 % group == 0 and page_size in (8, 16, 32, 64)
                     and self.prefill_attention == "tcgen05"):
                 # tcgen05/TMEM kernel; it answers "unsupported" for what it does not take
                 self.launches += 1
@@ -985,11 +994,12 @@ class CudaOps:
             if work and not done:
                 if self.timing is not None:
                     self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=True))
-                self._call("attention_prefill", "q3_paged_attention_prefill", "paged_attention_prefill",
+                self._call("attention_prefill", "q3_paged_attention_prefill_sink", "paged_attention_prefill",
                            _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                            block_table.shape[1], _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out),
                            step.num_seqs, work, num_heads, num_kv_heads, head_dim, page_size, float(scale),
-                           int(window or 0), 1)
+                           int(window or 0), 1, keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
+                           gate.stride(0) if gate is not None else 0)
             if step.num_single:
                 singles = [kv for kv, n in zip(step.host_kv_lens, qlens) if n == 1]
                 longest = max(singles)
@@ -998,7 +1008,8 @@ class CudaOps:
                     k_pages=k_pages, v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens,
                     cu_seqlens=step.cu_seqlens, out=out, page_size=page_size, scale=scale, window=window,
                     num_seqs=step.num_single, max_kv_len=longest, seq_list=step.single_seqs, step=step,
-                    num_splits=self.decode_slices_for(singles, num_kv_heads, head_dim, window))
+                    num_splits=self.decode_slices_for(singles, num_kv_heads, head_dim,
+                                                      window + keep_first if window else window), **extras)
             return out
         if self.timing is not None and step is not None:
             self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out))
@@ -1104,7 +1115,7 @@ class CudaOps:
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
                                max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None,
-                               merge_kernel=False, longest=None):
+                               merge_kernel=False, longest=None, keep_first=0, sink=None, gate=None):
         """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
         ``new_token`` (q_weight, k_weight, eps, cos, sin, optionally pairing): ``q`` is the raw q/k/v
         projection and the kernel also does the work of :meth:`qk_norm_rope_store` for the newest
@@ -1113,11 +1124,15 @@ class CudaOps:
         asks for the second kernel that callers without ticket words get (the bits are the same).
         ``num_splits`` is the slice count of the longest sequence (a shorter one gets fewer slices of
         about the same length); ``longest``: a device int32 holding the longest of the sequences'
-        lengths, when the caller has it (else every block works it out from ``kv_lens``)."""
+        lengths, when the caller has it (else every block works it out from ``kv_lens``).
+        ``keep_first``, ``sink``, ``gate``: as in :meth:`paged_attention` (not with ``new_token``)."""
         if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
             raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
+        keep_first = int(keep_first or 0) if window else 0
+        if new_token is not None and (keep_first or sink is not None or gate is not None):
+            raise KernelError("paged_attention_decode: kept first tokens, a sink or a gate do not go with new_token")
         if window:
-            max_kv_len = min(max_kv_len, int(window) + 63)
+            max_kv_len = min(max_kv_len, int(window) + keep_first + 63)
         splits = num_splits or self.decode_splits(num_seqs, num_kv_heads, max_kv_len, head_dim)
         mid_o = mid_lse = None
         tickets = None
@@ -1143,11 +1158,12 @@ class CudaOps:
                        _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
                        self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets), _ptr(longest))
             return out
-        self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
+        self._call("attention_decode", "q3_paged_attention_decode_sink", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                    num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits,
-                   _ptr(tickets), _ptr(longest))
+                   _ptr(tickets), _ptr(longest), keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
+                   gate.stride(0) if gate is not None else 0)
         return out
 
     # ---- matrix products ----------------------------------------------------------------

@@ -67,7 +67,28 @@ class SinkWindowAttention(Part):
     def kernel_groups(self):
         groups = ["rope_kv", "attention_generic"]
         groups += ["gemm_f32"] if self.ctx.dtype == torch.float32 else ["gemm_small_m", "gemm_stream"]
+        if self._specialised():
+            groups += ["attention_decode", "attention_prefill"]
         return groups
+
+    def _specialised(self) -> bool:
+        """Keys and values of one size that the split-KV decode kernel and the tensor-core prompt kernel
+        take (ops.paged_attention sends a dense output there), with the window's kept first tokens, the
+        sink and the gate."""
+        return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128)
+                and self.num_heads // self.num_kv_heads <= 16)
+
+    def _slices_key(self):
+        reach = self.window + self.keep_first if self.window else None  # the most keys a token sees
+        return ("decode_slices", self.num_kv_heads, self.dim, reach)
+
+    def step_choosers(self):
+        """Into how many slices the split-KV decode kernel cuts the longest sequence's keys."""
+        model = getattr(self.ops, "decode_slices_for", None)
+        if model is None or not self._specialised():
+            return {}
+        key = self._slices_key()
+        return {key: lambda kv_lens: model(kv_lens, key[1], key[2], key[3])}
 
     def cache_spec(self):
         return KVLayerSpec(self.num_kv_heads, self.dim, self.window, value_dim=self.vdim, keep_first=self.keep_first)
@@ -89,7 +110,7 @@ class SinkWindowAttention(Part):
                             v_pages=cache.v_pages, block_table=block_table, token_seq=step.token_seq,
                             positions=step.positions, out=ctx, page_size=cache.page_size, scale=self.scale,
                             window=self.window, step=step, value_dim=Dv, keep_first=self.keep_first, sink=self.sink,
-                            gate=gate)
+                            gate=gate, decode_slices=step.choices.get(self._slices_key()))
         return ops.linear(ctx, self.o_weight)
 
 

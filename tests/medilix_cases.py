@@ -349,13 +349,16 @@ def case_mixer_alone(dtype, ops, device, kind, *, T=45, page_size=8, cuts=(24, 1
     assert diff <= tol, f"{kind} mixer ({dtype}, {sizes}): off by {diff:.3g} (allowed {tol:.3g})"
 
 
-def case_attention_edges(dtype, ops, device, *, window=12, keep=3, page_size=8, heads=4, kv_heads=2, D=24, Dv=40, T=50):
+def case_attention_edges(dtype, ops, device, *, window=12, keep=3, page_size=8, heads=4, kv_heads=2, D=24, Dv=40, T=50,
+                         dense_out=False, decode_slices=None):
     """The attention kernel alone with one key that takes nearly all the weight when it is seen: at distance
     window - 1 it decides the output, at distance window it does not, unless it is one of the kept first
     tokens (the last kept one is seen from everywhere, the one after it is not); for queries inside a prompt
     portion and as a single decoded token; keys at a page's last row, first row and inside one.  Where the
     few keys are seen (the sequence's first tokens, a window of one) the sink takes a large share: the plain
-    output is far from a plain softmax's.  With a gate.  Pages are out of order and unused rows hold NaN."""
+    output is far from a plain softmax's.  With a gate.  Pages are out of order and unused rows hold NaN.
+    ``dense_out``: the output rows are not a slice of wider ones (what the kernels for keys and values of one
+    size want); ``decode_slices``: the single token's keys are cut into that many slices."""
     dt = TORCH[dtype]
     gen = torch.Generator().manual_seed(17)
     pages_needed = -(-T // page_size)
@@ -388,18 +391,20 @@ def case_attention_edges(dtype, ops, device, *, window=12, keep=3, page_size=8, 
             v_pages[table[j // page_size], :, j % page_size] = v[j].to(dt)
         for lo, hi in ((0, T), (qi - 1, qi + 1), (qi, qi + 1)):  # a whole prompt; a portion of two; one decoded token
             step = _step(list(range(lo, hi)), [0] * (hi - lo), [table], device)
-            wide = torch.zeros((hi - lo, heads * Dv + 16), dtype=dt, device=device)
+            pad = 0 if dense_out else 8
+            wide = torch.zeros((hi - lo, heads * Dv + 2 * pad), dtype=dt, device=device)
             qd = q[lo:hi].reshape(hi - lo, heads * D).to(device=device, dtype=dt).contiguous()
             ops.paged_attention(qd, qd.stride(0), num_heads=heads, num_kv_heads=kv_heads, head_dim=D, k_pages=k_pages,
                                 v_pages=v_pages, block_table=step.block_tables[0], token_seq=step.token_seq,
-                                positions=step.positions, out=wide[:, 8:8 + heads * Dv], page_size=page_size, scale=1.0,
+                                positions=step.positions, out=wide[:, pad:pad + heads * Dv], page_size=page_size, scale=1.0,
                                 window=win, step=step, value_dim=Dv, keep_first=kp, sink=0.0,
-                                gate=g[lo:hi].to(device=device, dtype=dt))
-            out = wide[:, 8:8 + heads * Dv].float().cpu().reshape(hi - lo, heads, Dv)
+                                gate=g[lo:hi].to(device=device, dtype=dt),
+                                **({"decode_slices": decode_slices} if decode_slices and hi - lo == 1 else {}))
+            out = wide[:, pad:pad + heads * Dv].float().cpu().reshape(hi - lo, heads, Dv)
             diff = float((out - want[lo:hi]).abs().max())
             tol = 2e-5 if dtype == "float32" else 3e-2
             assert diff <= tol, f"window {win} keep {kp}, query {qi}, key {kj}, tokens {lo}..{hi}: off by {diff:.3g}"
-            assert float(wide[:, :8].abs().max()) == 0 and float(wide[:, 8 + heads * Dv:].abs().max()) == 0
+            assert dense_out or (float(wide[:, :8].abs().max()) == 0 and float(wide[:, 8 + heads * Dv:].abs().max()) == 0)
 
 
 def _portion_steps(portion_sets, device, slots):

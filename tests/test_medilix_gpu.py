@@ -53,6 +53,13 @@ def test_attention_edges(ops, dtype):
     mc.case_attention_edges(dtype, ops, DEV, window=8, keep=1, page_size=8, heads=1, kv_heads=1, D=20, Dv=8)
     mc.case_attention_edges(dtype, ops, DEV, window=16, keep=5, page_size=16, heads=6, kv_heads=2, D=48, Dv=96, T=70)
     mc.case_attention_edges(dtype, ops, DEV, window=33, keep=16, page_size=16, heads=8, kv_heads=2, D=64, Dv=64, T=120)
+    # keys and values of one size, dense rows: in bfloat16 the split-KV and the tensor-core prompt kernels
+    mc.case_attention_edges(dtype, ops, DEV, window=33, keep=16, page_size=16, heads=8, kv_heads=2, D=64, Dv=64, T=120,
+                            dense_out=True)
+    mc.case_attention_edges(dtype, ops, DEV, window=150, keep=70, page_size=16, heads=4, kv_heads=1, D=128, Dv=128,
+                            T=330, dense_out=True, decode_slices=3)
+    mc.case_attention_edges(dtype, ops, DEV, window=70, keep=130, page_size=32, heads=2, kv_heads=2, D=64, Dv=64,
+                            T=300, dense_out=True, decode_slices=2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
