@@ -719,6 +719,91 @@ __global__ void grouped_norm_kernel(const void* __restrict__ pending, int parts,
   }
 }
 
+// The same with eight consecutive values a thread and 16-byte accesses (H and a group's size multiples of 8,
+// every row 16-byte aligned).  The arithmetic per value and the groups' sums are those of the kernel above.
+template <typename T>
+__global__ void grouped_norm_kernel_v8(const void* __restrict__ pending, int parts, long part_stride,
+                                       const T* __restrict__ more, float* __restrict__ resid,
+                                       const int* __restrict__ rows, const float* __restrict__ w,
+                                       const float* __restrict__ w2, T* __restrict__ out, long out_stride,
+                                       T* __restrict__ out2, int H, int groups, float eps, int write_resid) {
+  extern __shared__ __align__(16) float gvals[];
+  float* rstd = gvals + H;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const long src = rows ? rows[r] : r;
+  const T* prow = pending && !parts ? static_cast<const T*>(pending) + src * H : nullptr;
+  const float* frow = pending && parts ? static_cast<const float*>(pending) + src * H : nullptr;
+  const T* mrow = more ? more + src * H : nullptr;
+  float* rrow = resid + src * H;
+  T* orow = out + (long)r * out_stride;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8], a[8];
+    load8(rrow + i, v);
+    bool any = false;
+    if (frow) {
+      load8(frow + i, a);
+      for (int p = 1; p < parts; ++p) {
+        float b[8];
+        load8(frow + p * part_stride + i, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += b[e];
+      }
+      any = true;
+    } else if (prow) {
+      load8(prow + i, a);
+      any = true;
+    }
+    if (mrow) {
+      float b[8];
+      load8(mrow + i, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = any ? a[e] + b[e] : b[e];
+      any = true;
+    }
+    if (any) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = v[e] + a[e];
+    }
+    if (write_resid) store8(rrow + i, v);
+    if (w) store8(gvals + i, v); else store8(orow + i, v);
+  }
+  if (!w) return;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const int Hg = H / groups;
+  for (int g = warp; g < groups; g += nwarp) {
+    float ss = 0.f;
+    for (int i = lane; i < Hg; i += 32) {
+      const float v = gvals[g * Hg + i];
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) rstd[g] = rsqrtf(ss / (float)Hg + eps);
+  }
+  __syncthreads();
+  T* orow2 = out2 ? out2 + (long)r * H : nullptr;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8], ww[8], y[8];
+    load8(gvals + i, v);
+    const float rs = rstd[i / Hg];
+    load8(w + i, ww);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[e] = v[e] * rs;
+      y[e] = v[e] * ww[e];
+    }
+    store8(orow + i, y);
+    if (orow2) {
+      load8(w2 + i, ww);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = v[e] * ww[e];
+      store8(orow2 + i, y);
+    }
+  }
+}
+
 // pending: `dtype` [*, H] when pending_parts is 0, else fp32 planes part_stride elements apart (or null);
 // more: `dtype` [*, H] or null; resid fp32 [*, H]; out rows out_stride elements apart; out2 dense or null
 // (needs w2); w null: out gets the sum itself.
@@ -733,6 +818,27 @@ Q3_EXPORT int q3_grouped_norm(int dtype, const void* pending, int pending_parts,
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   cudaError_t e;
+  const uintptr_t bits = (uintptr_t)pending | (uintptr_t)more | (uintptr_t)resid | (uintptr_t)w | (uintptr_t)w2 |
+                         (uintptr_t)out | (uintptr_t)out2;
+  const bool wide = H % 8 == 0 && (H / groups) % 8 == 0 && out_stride % 8 == 0 && part_stride % 8 == 0 && !(bits & 15) &&
+                    (dtype == Q3_DTYPE_F32 || dtype == Q3_DTYPE_BF16);
+  if (wide) {
+    const int vthreads = H >= 2048 ? 256 : (H >= 512 ? 64 : 32);
+    if (dtype == Q3_DTYPE_F32) {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(grouped_norm_kernel_v8<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = launch_pdl(grouped_norm_kernel_v8<float>, dim3(num_rows), dim3(vthreads), smem, stream, pending,
+                     pending_parts, part_stride, (const float*)more, resid, rows, w, w2, (float*)out, out_stride,
+                     (float*)out2, H, groups, eps, write_resid);
+    } else {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(grouped_norm_kernel_v8<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = launch_pdl(grouped_norm_kernel_v8<bf16>, dim3(num_rows), dim3(vthreads), smem, stream, pending,
+                     pending_parts, part_stride, (const bf16*)more, resid, rows, w, w2, (bf16*)out, out_stride,
+                     (bf16*)out2, H, groups, eps, write_resid);
+    }
+    return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+  }
   if (dtype == Q3_DTYPE_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(grouped_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

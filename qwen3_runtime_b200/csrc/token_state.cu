@@ -19,7 +19,7 @@ __global__ void bigram_embed_kernel(const int* __restrict__ ids, const T* __rest
                                     const int* __restrict__ prev_state, const int* __restrict__ positions,
                                     const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                                     const int* __restrict__ state_slots, float* __restrict__ out,
-                                    T* __restrict__ copy, long copy_stride, int W, int vocab) {
+                                    T* __restrict__ copy, long copy_stride, int W, int vocab, int wide) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -36,6 +36,22 @@ __global__ void bigram_embed_kernel(const int* __restrict__ ids, const T* __rest
       if (row < 0) row += buckets;
     }
     brow = bigram + row * W;
+  }
+  if (wide) {  // rows of a multiple of 8 values, 16-byte aligned: eight values a thread
+    for (int i = threadIdx.x * 8; i < W; i += blockDim.x * 8) {
+      float v[8], b[8];
+      load8(erow + i, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= scale;
+      if (brow) {
+        load8(brow + i, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += b[e];
+      }
+      store8(out + (long)t * W + i, v);
+      if (copy) store8(copy + (long)t * copy_stride + i, v);
+    }
+    return;
   }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float v = to_f32(erow[i]) * scale;
@@ -67,16 +83,18 @@ Q3_EXPORT int q3_bigram_embed(int dtype, const int* ids, const void* embed, floa
   if (bigram && (buckets < 1 || !prev_state || !positions || !token_seq || !cu_seqlens || !state_slots))
     return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
-  const int threads = W >= 1024 ? 256 : 128;
+  const uintptr_t bits = (uintptr_t)embed | (uintptr_t)bigram | (uintptr_t)out | (uintptr_t)copy;
+  const int wide = W % 8 == 0 && copy_stride % 8 == 0 && !(bits & 15);
+  const int threads = wide ? (W >= 2048 ? 256 : (W >= 512 ? 64 : 32)) : (W >= 1024 ? 256 : 128);
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32)
     e = launch_pdl(bigram_embed_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, ids, (const float*)embed,
                    scale, (const float*)bigram, buckets, mul_prev, mul_cur, (const int*)prev_state, positions,
-                   token_seq, cu_seqlens, state_slots, out, (float*)copy, copy_stride, W, vocab);
+                   token_seq, cu_seqlens, state_slots, out, (float*)copy, copy_stride, W, vocab, wide);
   else if (dtype == Q3_DTYPE_BF16)
     e = launch_pdl(bigram_embed_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, ids, (const bf16*)embed,
                    scale, (const bf16*)bigram, buckets, mul_prev, mul_cur, (const int*)prev_state, positions,
-                   token_seq, cu_seqlens, state_slots, out, (bf16*)copy, copy_stride, W, vocab);
+                   token_seq, cu_seqlens, state_slots, out, (bf16*)copy, copy_stride, W, vocab, wide);
   else
     return Q3_ERR_ARGUMENT;
   if (e != cudaSuccess) return Q3_ERR_LAUNCH;
@@ -92,7 +110,8 @@ template <typename T>
 __global__ void token_shift_mix_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ mu, int n,
                                        const float* __restrict__ state, const int* __restrict__ positions,
                                        const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
-                                       const int* __restrict__ state_slots, T* __restrict__ out, long plane, int W) {
+                                       const int* __restrict__ state_slots, T* __restrict__ out, long plane, int W,
+                                       int wide) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -102,6 +121,29 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ h, long h_stride, c
   const T* cur = h + (long)t * h_stride;
   const T* before = h + (long)(t - 1) * h_stride;
   const float* kept = state + (long)state_slots[b] * W;
+  if (wide) {  // rows of a multiple of 8 values, 16-byte aligned: eight values a thread
+    for (int i = threadIdx.x * 8; i < W; i += blockDim.x * 8) {
+      float x[8], p[8], m[8], y[8];
+      load8(cur + i, x);
+      if (first) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) p[e] = 0.f;
+      } else if (inside) {
+        load8(before + i, p);
+      } else {
+        load8(kept + i, p);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) p[e] -= x[e];
+      for (int s = 0; s < n; ++s) {
+        load8(mu + (long)s * W + i, m);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = fmaf(p[e], m[e], x[e]);
+        store8(out + s * plane + (long)t * W + i, y);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float x = to_f32(cur[i]);
     const float p = first ? 0.f : (inside ? to_f32(before[i]) : kept[i]);
@@ -131,18 +173,23 @@ Q3_EXPORT int q3_token_shift_mix(int dtype, const void* h, long h_stride, const 
   if (!h || !mu || !state || !positions || !token_seq || !cu_seqlens || !state_slots || !out || n < 1 || W < 1)
     return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
+  const uintptr_t bits = (uintptr_t)h | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)out;
+  const int wide = W % 8 == 0 && h_stride % 8 == 0 && !(bits & 15);
   const int threads = W >= 1024 ? 256 : 128;
+  const int mix_threads = wide ? (W >= 2048 ? 256 : (W >= 512 ? 64 : 32)) : threads;
   const long plane = (long)num_tokens * W;
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32) {
-    e = launch_pdl(token_shift_mix_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)h, h_stride,
-                   mu, n, (const float*)state, positions, token_seq, cu_seqlens, state_slots, (float*)out, plane, W);
+    e = launch_pdl(token_shift_mix_kernel<float>, dim3(num_tokens), dim3(mix_threads), 0, stream, (const float*)h,
+                   h_stride, mu, n, (const float*)state, positions, token_seq, cu_seqlens, state_slots, (float*)out,
+                   plane, W, wide);
     if (e == cudaSuccess)
       e = launch_pdl(token_shift_update_kernel<float>, dim3(num_seqs), dim3(threads), 0, stream, (const float*)h,
                      h_stride, cu_seqlens, state_slots, state, W);
   } else if (dtype == Q3_DTYPE_BF16) {
-    e = launch_pdl(token_shift_mix_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)h, h_stride,
-                   mu, n, (const float*)state, positions, token_seq, cu_seqlens, state_slots, (bf16*)out, plane, W);
+    e = launch_pdl(token_shift_mix_kernel<bf16>, dim3(num_tokens), dim3(mix_threads), 0, stream, (const bf16*)h,
+                   h_stride, mu, n, (const float*)state, positions, token_seq, cu_seqlens, state_slots, (bf16*)out,
+                   plane, W, wide);
     if (e == cudaSuccess)
       e = launch_pdl(token_shift_update_kernel<bf16>, dim3(num_seqs), dim3(threads), 0, stream, (const bf16*)h,
                      h_stride, cu_seqlens, state_slots, state, W);

@@ -67,7 +67,10 @@ def test_token_state_and_norm(ops, dtype):
     mc.case_token_state(dtype, ops, DEV)
     mc.case_token_state(dtype, ops, DEV, buckets=1, mul_prev=0, mul_cur=1)
     mc.case_token_state(dtype, ops, DEV, W=200, vocab=300, buckets=1009, mul_prev=37, mul_cur=11)
+    mc.case_token_state(dtype, ops, DEV, W=36)  # rows that are no multiple of 8 values: one value a thread
     mc.case_grouped_norm(dtype, ops, DEV)
+    mc.case_grouped_norm(dtype, ops, DEV, W=240)  # groups of a multiple of 8 values: eight values a thread
+    mc.case_grouped_norm(dtype, ops, DEV, W=4080)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
