@@ -68,14 +68,14 @@ class SinkWindowAttention(Part):
         groups = ["rope_kv", "attention_generic"]
         groups += ["gemm_f32"] if self.ctx.dtype == torch.float32 else ["gemm_small_m", "gemm_stream"]
         if self._specialised():
-            groups += ["attention_decode", "attention_prefill"]
+            groups += ["attention_decode"] + (["attention_prefill"] if self.dim in (64, 128) else [])
         return groups
 
     def _specialised(self) -> bool:
-        """Keys and values of one size that the split-KV decode kernel and the tensor-core prompt kernel
-        take (ops.paged_attention sends a dense output there), with the window's kept first tokens, the
+        """Keys and values of one size that the split-KV decode kernel (64, 128, 256) and the tensor-core prompt
+        kernel (64, 128) take (ops.paged_attention sends a dense output there), with the window's kept first tokens, the
         sink and the gate."""
-        return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128)
+        return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128, 256)
                 and self.num_heads // self.num_kv_heads <= 16)
 
     def _slices_key(self):

@@ -60,6 +60,8 @@ def test_attention_edges(ops, dtype):
                             T=330, dense_out=True, decode_slices=3)
     mc.case_attention_edges(dtype, ops, DEV, window=70, keep=130, page_size=32, heads=2, kv_heads=2, D=64, Dv=64,
                             T=300, dense_out=True, decode_slices=2)
+    mc.case_attention_edges(dtype, ops, DEV, window=70, keep=9, page_size=16, heads=2, kv_heads=1, D=256, Dv=256,
+                            T=160, dense_out=True, decode_slices=2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -147,3 +149,29 @@ def test_trace_replay_program_on_a_medilix_folder(tmp_path, ops):
     got1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, V))
     assert float((got0 - want["a"][[0, 12]]).abs().max()) <= tol
     assert float((got1 - want["a"][[19]]).abs().max()) <= tol
+
+
+def test_command_line_on_a_medilix_folder(tmp_path):
+    """``python -m qwen3_runtime_b200.cli`` generates greedily from a Medilix folder what the plain model does."""
+    import os
+    import subprocess
+    import sys
+
+    import plain_medilix as pl
+
+    folder = mc.make_dir(tmp_path, "A")
+    raw, t = mc.read_dir(folder)
+    prompt = [5, 6, 7, 8, 9]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "qwen3_runtime_b200.cli", "--model", str(folder), "--max-tokens", "6", "--dtype",
+           "float32", "--prompt-tokens", *map(str, prompt), "--num-kv-blocks", "16", "--no-cuda-graph"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=root, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = dict(line.split(" ", 1) for line in proc.stdout.strip().splitlines())
+    got = [int(x) for x in lines["runtime"].strip("[]").split(",")]
+    assert len(got) == 6
+    seq = list(prompt)
+    for tok in got:  # every token is the plain model's best (or within float32 rounding of it) given the tokens before
+        row = pl.forward(raw, t, seq)[-1]
+        assert float(row.max() - row[tok]) <= 1e-4 * max(1.0, float(row.abs().max()))
+        seq.append(tok)
