@@ -678,6 +678,33 @@ Q3_EXPORT int q3_paged_attention_decode_sink(const void* q, int q_stride, const 
 // null.  The key and value of the newest token are written to their pages; q is not written
 // back.  `error_word` (may be null) is set to Q3_ERR_POSITION if a newest position lies beyond
 // the tables; that token is then left unrotated and the result is invalid.
+// (keep_first, has_sink, sink, gate, gate_stride: as in q3_paged_attention_decode_sink.)
+Q3_EXPORT int q3_paged_attention_decode_fused_sink(const void* qkv, int q_stride, void* kpages, void* vpages,
+                                                   const int* block_table, int max_pages, const int* kv_lens,
+                                                   const int* cu_seqlens, const int* seq_list, void* out,
+                                                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D,
+                                                   int ps, float scale, int window, int num_splits, const float* q_w,
+                                                   const float* k_w, float eps, const float* cos_t,
+                                                   const float* sin_t, int max_pos, int pairing, int* error_word,
+                                                   int* tickets, const int* longest_len, int keep_first, int has_sink,
+                                                   float sink, const void* gate, int gate_stride,
+                                                   cudaStream_t stream) {
+  if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
+  if (keep_first < 0 || (gate && gate_stride < nq * D)) return Q3_ERR_ARGUMENT;
+  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
+                         (uintptr_t)cos_t | (uintptr_t)sin_t;
+  if (bits & 15) return Q3_ERR_UNSUPPORTED;
+  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing};
+  Extras ex;
+  ex.keep = window > 0 ? keep_first : 0;
+  ex.sink_log2 = has_sink ? sink * 1.4426950408889634f : -INFINITY;
+  ex.gate = (const bf16*)gate;
+  ex.gate_stride = gate_stride;
+  return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
+                               out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt,
+                               error_word, tickets, longest_len, stream, ex);
+}
+
 Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, void* kpages, void* vpages,
                                               const int* block_table, int max_pages, const int* kv_lens,
                                               const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
@@ -686,14 +713,10 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
                                               const float* k_w, float eps, const float* cos_t, const float* sin_t,
                                               int max_pos, int pairing, int* error_word, int* tickets,
                                               const int* longest_len, cudaStream_t stream) {
-  if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
-  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
-                         (uintptr_t)cos_t | (uintptr_t)sin_t;
-  if (bits & 15) return Q3_ERR_UNSUPPORTED;
-  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing};
-  return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
-                               out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt,
-                               error_word, tickets, longest_len, stream);
+  return q3_paged_attention_decode_fused_sink(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens,
+                                              cu_seqlens, seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale,
+                                              window, num_splits, q_w, k_w, eps, cos_t, sin_t, max_pos, pairing,
+                                              error_word, tickets, longest_len, 0, 0, 0.f, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

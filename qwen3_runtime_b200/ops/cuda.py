@@ -152,6 +152,11 @@ _SIGNATURES = {
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
                                             c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "q3_paged_attention_decode_fused_sink": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                 c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
+                                                 c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_int, c_float, c_void_p, c_int, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -1125,12 +1130,10 @@ class CudaOps:
         ``num_splits`` is the slice count of the longest sequence (a shorter one gets fewer slices of
         about the same length); ``longest``: a device int32 holding the longest of the sequences'
         lengths, when the caller has it (else every block works it out from ``kv_lens``).
-        ``keep_first``, ``sink``, ``gate``: as in :meth:`paged_attention` (not with ``new_token``)."""
+        ``keep_first``, ``sink``, ``gate``: as in :meth:`paged_attention`."""
         if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
             raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
         keep_first = int(keep_first or 0) if window else 0
-        if new_token is not None and (keep_first or sink is not None or gate is not None):
-            raise KernelError("paged_attention_decode: kept first tokens, a sink or a gate do not go with new_token")
         if window:
             max_kv_len = min(max_kv_len, int(window) + keep_first + 63)
         splits = num_splits or self.decode_splits(num_seqs, num_kv_heads, max_kv_len, head_dim)
@@ -1150,13 +1153,15 @@ class CudaOps:
             self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=False))
         if new_token is not None:
             cos, sin = new_token["cos"], new_token["sin"]
-            self._call("attention_decode", "q3_paged_attention_decode_fused", "paged_attention_decode_fused",
+            self._call("attention_decode", "q3_paged_attention_decode_fused_sink", "paged_attention_decode_fused",
                        _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                        _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                        num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
                        splits, _ptr(new_token["q_weight"]), _ptr(new_token["k_weight"]), float(new_token["eps"]),
                        _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
-                       self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets), _ptr(longest))
+                       self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets), _ptr(longest),
+                       keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
+                       gate.stride(0) if gate is not None else 0)
             return out
         self._call("attention_decode", "q3_paged_attention_decode_sink", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],

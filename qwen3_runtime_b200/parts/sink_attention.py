@@ -99,13 +99,30 @@ class SinkWindowAttention(Part):
         s = self.starts
         proj = ops.linear(h, self.in_weight)
         block_table = step.block_tables[cache.paged_index]
+        ctx = torch.empty((h.shape[0], H * Dv), dtype=h.dtype, device=h.device)
+        gate = proj[:, s[3]:s[3] + H * Dv] if self.gate else None
+        fusable = getattr(ops, "decode_new_token_ok", None)
+        if (fusable is not None and step.decode_only and cache.writes and self._specialised()
+                and s[1] == H * D and s[2] == (H + G) * D  # q, k and v heads side by side, as that kernel reads them
+                and fusable(proj, num_heads=H, num_kv_heads=G, head_dim=D, cos=None, q_weight=self.q_norm,
+                            k_weight=self.k_norm)):
+            # one kernel: unit norm of the newest q and k, cache write, split-KV attention with sink and gate
+            width = step.captured_width
+            ops.paged_attention_decode(
+                proj, proj.stride(0), num_heads=H, num_kv_heads=G, head_dim=D, k_pages=cache.k_pages,
+                v_pages=cache.v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
+                out=ctx, page_size=cache.page_size, scale=self.scale, window=self.window, num_seqs=step.num_seqs,
+                max_kv_len=width * cache.page_size or step.max_kv_len,
+                new_token=dict(q_weight=self.q_norm, k_weight=self.k_norm,
+                               eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos=None, sin=None),
+                num_splits=step.choices.get(self._slices_key()), longest=step.kv_longest, step=step,
+                keep_first=self.keep_first, sink=self.sink, gate=gate)
+            return ops.linear(ctx, self.o_weight)
         ops.qk_norm_store(proj, num_heads=H, num_kv_heads=G, head_dim=D, value_dim=Dv, k_start=s[1], v_start=s[2],
                           q_weight=self.q_norm, k_weight=self.k_norm,
                           eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, positions=step.positions,
                           token_seq=step.token_seq, block_table=block_table, k_pages=cache.k_pages,
                           v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes)
-        ctx = torch.empty((h.shape[0], H * Dv), dtype=h.dtype, device=h.device)
-        gate = proj[:, s[3]:s[3] + H * Dv] if self.gate else None
         ops.paged_attention(proj, proj.stride(0), num_heads=H, num_kv_heads=G, head_dim=D, k_pages=cache.k_pages,
                             v_pages=cache.v_pages, block_table=block_table, token_seq=step.token_seq,
                             positions=step.positions, out=ctx, page_size=cache.page_size, scale=self.scale,
