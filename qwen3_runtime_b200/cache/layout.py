@@ -24,13 +24,16 @@ from .manager import GroupSpec
 class KVLayerSpec:
     """``value_dim``: values have a size of their own (None: the keys' ``head_dim``); keys and values
     are then two device tensors, ``[layers, pages + 1, kv_heads, page_size, head_dim | value_dim]``.
-    ``keep_first``: with a window, the sequence's first ``keep_first`` tokens stay readable as well."""
+    ``keep_first``: with a window, the sequence's first ``keep_first`` tokens stay readable as well.
+    ``chunk``: a token reads only the keys of its own chunk of that many tokens (counted from the sequence's
+    first token); pages wholly before the current chunk are given back."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
     keep_first: int = 0
+    chunk: int | None = None
 
     @property
     def split(self) -> bool:
@@ -92,8 +95,12 @@ class CacheLayout:
         self.groups: list[GroupLayout] = []
         for spec, ids in buckets.items():
             if isinstance(spec, (KVLayerSpec, LatentLayerSpec)):
-                gs = (GroupSpec("window", spec.window, getattr(spec, "keep_first", 0)) if spec.window
-                      else GroupSpec("full"))
+                if spec.window:
+                    gs = GroupSpec("window", spec.window, getattr(spec, "keep_first", 0))
+                elif getattr(spec, "chunk", None):
+                    gs = GroupSpec("chunk", chunk=spec.chunk)
+                else:
+                    gs = GroupSpec("full")
             elif isinstance(spec, StateLayerSpec):
                 gs = GroupSpec("state")
             else:
@@ -149,7 +156,7 @@ class CacheLayout:
             return counts
         spent, open_bytes = 0, 0
         for i, gi in enumerate(self.paged_groups):
-            window = self.groups[gi].spec.window
+            window = self.groups[gi].spec.window or self.groups[gi].spec.chunk  # the most keys a request holds
             if window:
                 kept = -(-self.groups[gi].spec.keep_first // page_size)
                 cap = max_num_seqs * (-(-(window + max_step_tokens) // page_size) + 2 + kept)
@@ -159,5 +166,6 @@ class CacheLayout:
                 open_bytes += per[i]
         if open_bytes:
             full = int((budget_bytes - spent) // open_bytes)
-            counts = [c if self.groups[gi].spec.window else full for c, gi in zip(counts, self.paged_groups)]
+            counts = [c if (self.groups[gi].spec.window or self.groups[gi].spec.chunk) else full
+                      for c, gi in zip(counts, self.paged_groups)]
         return counts

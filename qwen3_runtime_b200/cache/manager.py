@@ -6,6 +6,9 @@ Layers are put into *groups* by what they need from the cache:
 * ``window`` -- only the last ``window`` keys are read, so pages that the window has
   passed are given back while the request is still running (except the pages that hold the
   sequence's first ``keep_first`` tokens, when the group keeps those readable);
+* ``chunk``  -- a token reads keys of its own chunk only (chunks of ``chunk`` tokens counted from the
+  sequence's first token), so the pages that lie wholly before the chunk the next token falls in are
+  given back;
 * ``state``  -- a fixed-size slot per request (recurrent or convolution state), no pages.
 
 Each paged group has pages of its own (its own allocator and device tensors) and
@@ -36,17 +39,20 @@ class CacheError(RuntimeError):
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """What one group of cache layers needs.  ``kind``: full | window | state."""
+    """What one group of cache layers needs.  ``kind``: full | window | chunk | state."""
 
     kind: str
     window: int | None = None
     keep_first: int = 0  # a window group: the first tokens of a sequence that stay readable too
+    chunk: int | None = None  # a chunk group: the chunks' size
 
     def __post_init__(self) -> None:
-        if self.kind not in ("full", "window", "state"):
+        if self.kind not in ("full", "window", "chunk", "state"):
             raise ValueError(f"unknown cache group kind {self.kind!r}")
         if self.kind == "window" and (self.window is None or self.window < 1):
             raise ValueError("a window group needs window >= 1")
+        if self.kind == "chunk" and (self.chunk is None or self.chunk < 1):
+            raise ValueError("a chunk group needs chunk >= 1")
 
     @property
     def paged(self) -> bool:
@@ -227,11 +233,16 @@ class CacheManager:
         rc.num_computed = end
         for gi, table, alloc in zip(self.paged_groups, rc.tables, self.allocators):
             group = self.groups[gi]
-            if group.kind != "window":
+            if group.kind == "chunk":
+                # the next query sits at position >= end and reads no key before the chunk that holds `end`
+                first_needed = end // group.chunk * group.chunk
+                kept_pages = 0
+            elif group.kind == "window":
+                # the next query sits at position >= end and reads keys > end - window
+                first_needed = max(0, end - group.window + 1)
+                kept_pages = -(-group.keep_first // self.page_size)  # pages that hold a kept first token
+            else:
                 continue
-            # the next query sits at position >= end and reads keys > end - window
-            first_needed = max(0, end - group.window + 1)
-            kept_pages = -(-group.keep_first // self.page_size)  # pages that hold a kept first token
             for idx in range(kept_pages, min(first_needed // self.page_size, len(table))):
                 if table[idx] != FREED:
                     alloc.release(table[idx])

@@ -2,6 +2,7 @@ from .engine_config import EngineConfig, canonical_dtype
 from .logesun_config import LogesunConfig
 from .medilix_config import MedilixConfig
 from .puladra_config import PuladraConfig
+from .tabisun_config import TabisunConfig
 from .model_config import ConfigError, Qwen3Config
 from .registry import (
     Architecture,
@@ -29,6 +30,7 @@ __all__ = [
     "PartSpec",
     "PuladraConfig",
     "Qwen3Config",
+    "TabisunConfig",
     "canonical_dtype",
     "load_config",
     "read_config_json",

@@ -65,6 +65,8 @@ class ModelSpec:
     embed_name: str = "model.embed_tokens.weight"
     head_name: str = "lm_head.weight"
     block_prefix: str = "model.layers.{index}."
+    # each block's own prefix, for models whose stored blocks are not numbered 0, 1, 2, ... (None: block_prefix)
+    block_names: tuple[str, ...] | None = None
     final_norm_prefix: str = "model.norm."
     # the head's epilogue: logits * logit_scale, then (if set) softcap * tanh(logits / softcap)
     logit_scale: float = 1.0
@@ -81,6 +83,8 @@ class ModelSpec:
     def __post_init__(self) -> None:
         if self.logit_softcap is not None and not self.logit_softcap > 0:
             raise ValueError("logit_softcap must be positive (or None)")
+        if self.block_names is not None and len(self.block_names) != len(self.blocks):
+            raise ValueError("block_names: one prefix per block")
         writers: set[int] = set()
         for run in self.order:
             if not 0 <= run.block < len(self.blocks):
@@ -95,6 +99,10 @@ class ModelSpec:
                 raise ValueError(f"run entry adds a row of {run.add_row[0]!r}, which is no shared table of the model")
             if run.mix_source is not None and run.mix_source not in {name for name, _s, _k in self.shared_tables}:
                 raise ValueError(f"run entry mixes through {run.mix_source!r}, which is no shared table of the model")
+
+    def prefix_of(self, index: int) -> str:
+        """The prefix of block ``index``'s stored tensors."""
+        return self.block_names[index] if self.block_names is not None else self.block_prefix.format(index=index)
 
     @staticmethod
     def sequential_order(num_blocks: int) -> tuple[LayerRun, ...]:

@@ -8,8 +8,9 @@
 //   latent_attention        causal attention of every token over its sequence's rows, with an
 //                           optional window and an optional per-head sink in the denominator
 //
-// Rotation: pair i = elements (2i, 2i + 1), angle = float(position) * inv_freq[i] in fp32, exact
-// cosf/sinf; elements beyond 2 * pairs pass unchanged.  All norms, scores and softmax are fp32.
+// Rotation: pair i = elements (2i, 2i + 1) (pairing 1) or (i, i + pairs) (pairing 0), angle =
+// float(position) * inv_freq[i] in fp32, exact cosf/sinf, both multiplied by `magnitude`; elements beyond
+// 2 * pairs pass unchanged.  All norms, scores and softmax are fp32.
 #include "common.cuh"
 
 // ---- query latent norm, key latent norm, key rotation, cache write -------------------------------
@@ -22,7 +23,8 @@ __global__ void latent_norm_rope_store_kernel(const T* __restrict__ in, long in_
                                               const float* __restrict__ inv_freq, int pairs,
                                               const int* __restrict__ positions, const int* __restrict__ token_seq,
                                               const int* __restrict__ block_table, int max_pages,
-                                              T* __restrict__ pages, int ps, int write, T* __restrict__ q_out) {
+                                              T* __restrict__ pages, int ps, int write, T* __restrict__ q_out,
+                                              int pairing, float magnitude) {
   __shared__ float red[33];
   pdl_wait();
   pdl_launch_dependents();
@@ -37,7 +39,7 @@ __global__ void latent_norm_rope_store_kernel(const T* __restrict__ in, long in_
     const float c = to_f32(row[q_rank + i]);
     sc += c * c;
   }
-  const float rq = rsqrtf(block_sum(sq, red) / (float)q_rank + eps);
+  const float rq = q_rank ? rsqrtf(block_sum(sq, red) / (float)q_rank + eps) : 0.f;
   const float rc = rsqrtf(block_sum(sc, red) / (float)kv_rank + eps);
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
     q_out[(long)t * q_rank + i] = from_f32<T>((to_f32(row[i]) * rq) * q_w[i]);
@@ -49,6 +51,21 @@ __global__ void latent_norm_rope_store_kernel(const T* __restrict__ in, long in_
   for (int i = threadIdx.x; i < kv_rank; i += blockDim.x)
     dst[i] = from_f32<T>((to_f32(row[q_rank + i]) * rc) * kv_w[i]);
   const T* k = row + q_rank + kv_rank;
+  if (!pairing) {  // halves: pair i = (i, i + pairs); the rest is copied
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
+      float y = to_f32(k[i]);
+      if (i < 2 * pairs) {
+        const bool first = i < pairs;
+        const int pi = first ? i : i - pairs;
+        const float other = to_f32(k[first ? i + pairs : i - pairs]);
+        const float ang = (float)p * inv_freq[pi];
+        const float cs = cosf(ang) * magnitude, sn = sinf(ang) * magnitude;
+        y = first ? y * cs - other * sn : y * cs + other * sn;
+      }
+      dst[kv_rank + i] = from_f32<T>(y);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < (rot_dim + 1) / 2; i += blockDim.x) {
     const float u = to_f32(k[2 * i]);
     if (2 * i + 1 >= rot_dim) {
@@ -57,7 +74,7 @@ __global__ void latent_norm_rope_store_kernel(const T* __restrict__ in, long in_
       const float v = to_f32(k[2 * i + 1]);
       if (i < pairs) {
         const float ang = (float)p * inv_freq[i];
-        const float cs = cosf(ang), sn = sinf(ang);
+        const float cs = cosf(ang) * magnitude, sn = sinf(ang) * magnitude;
         dst[kv_rank + 2 * i] = from_f32<T>(u * cs - v * sn);
         dst[kv_rank + 2 * i + 1] = from_f32<T>(v * cs + u * sn);
       } else {
@@ -72,8 +89,10 @@ Q3_EXPORT int q3_latent_norm_rope_store(int dtype, const void* in, long in_strid
                                         const float* q_w, const float* kv_w, float eps, const float* inv_freq,
                                         int pairs, const int* positions, const int* token_seq,
                                         const int* block_table, int max_pages, void* pages, int ps, int num_tokens,
-                                        int write, void* q_out, cudaStream_t stream) {
-  if (!in || !q_w || !kv_w || !q_out || q_rank < 1 || kv_rank < 1 || rot_dim < 0 || ps < 1) return Q3_ERR_ARGUMENT;
+                                        int write, void* q_out, int pairing, float magnitude,
+                                        cudaStream_t stream) {
+  if (!in || !kv_w || q_rank < 0 || kv_rank < 1 || rot_dim < 0 || ps < 1) return Q3_ERR_ARGUMENT;
+  if ((q_rank && (!q_w || !q_out)) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
   if (write && (!positions || !token_seq || !block_table || !pages)) return Q3_ERR_ARGUMENT;
   if (pairs < 0 || 2 * pairs > rot_dim || (pairs && !inv_freq)) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
@@ -81,11 +100,11 @@ Q3_EXPORT int q3_latent_norm_rope_store(int dtype, const void* in, long in_strid
   if (dtype == Q3_DTYPE_F32)
     e = launch_pdl(latent_norm_rope_store_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (const float*)in,
                    in_stride, q_rank, kv_rank, rot_dim, q_w, kv_w, eps, inv_freq, pairs, positions, token_seq,
-                   block_table, max_pages, (float*)pages, ps, write, (float*)q_out);
+                   block_table, max_pages, (float*)pages, ps, write, (float*)q_out, pairing, magnitude);
   else if (dtype == Q3_DTYPE_BF16)
     e = launch_pdl(latent_norm_rope_store_kernel<bf16>, dim3(num_tokens), dim3(128), 0, stream, (const bf16*)in,
                    in_stride, q_rank, kv_rank, rot_dim, q_w, kv_w, eps, inv_freq, pairs, positions, token_seq,
-                   block_table, max_pages, (bf16*)pages, ps, write, (bf16*)q_out);
+                   block_table, max_pages, (bf16*)pages, ps, write, (bf16*)q_out, pairing, magnitude);
   else
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
@@ -95,9 +114,28 @@ Q3_EXPORT int q3_latent_norm_rope_store(int dtype, const void* in, long in_strid
 template <typename T>
 __global__ void rotate_heads_kernel(const T* __restrict__ x, long xs_t, long xs_h, T* __restrict__ out, long os_t,
                                     long os_h, const int* __restrict__ positions,
-                                    const float* __restrict__ inv_freq, int pairs, int n, int H, long total) {
+                                    const float* __restrict__ inv_freq, int pairs, int n, int H, long total,
+                                    int pairing, float magnitude) {
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
+  if (!pairing) {  // halves: one thread per element, pair i = (i, i + pairs)
+    const int i = (int)(idx % n);
+    const long th = idx / n;
+    const int h = (int)(th % H);
+    const long t = th / H;
+    const T* src = x + t * xs_t + h * xs_h;
+    float y = to_f32(src[i]);
+    if (i < 2 * pairs) {
+      const bool first = i < pairs;
+      const int pi = first ? i : i - pairs;
+      const float other = to_f32(src[first ? i + pairs : i - pairs]);
+      const float ang = (float)positions[t] * inv_freq[pi];
+      const float cs = cosf(ang) * magnitude, sn = sinf(ang) * magnitude;
+      y = first ? y * cs - other * sn : y * cs + other * sn;
+    }
+    out[t * os_t + h * os_h + i] = from_f32<T>(y);
+    return;
+  }
   const int half = (n + 1) / 2;
   const int i = (int)(idx % half);
   const long th = idx / half;
@@ -113,7 +151,7 @@ __global__ void rotate_heads_kernel(const T* __restrict__ x, long xs_t, long xs_
   const float v = to_f32(src[2 * i + 1]);
   if (i < pairs) {
     const float ang = (float)positions[t] * inv_freq[i];
-    const float cs = cosf(ang), sn = sinf(ang);
+    const float cs = cosf(ang) * magnitude, sn = sinf(ang) * magnitude;
     dst[2 * i] = from_f32<T>(u * cs - v * sn);
     dst[2 * i + 1] = from_f32<T>(v * cs + u * sn);
   } else {
@@ -124,18 +162,19 @@ __global__ void rotate_heads_kernel(const T* __restrict__ x, long xs_t, long xs_
 
 Q3_EXPORT int q3_rotate_heads(int dtype, const void* x, long xs_t, long xs_h, void* out, long os_t, long os_h,
                               const int* positions, const float* inv_freq, int pairs, int n, int H, int num_tokens,
-                              cudaStream_t stream) {
+                              int pairing, float magnitude, cudaStream_t stream) {
   if (!x || !out || n < 1 || H < 1 || pairs < 0 || 2 * pairs > n) return Q3_ERR_ARGUMENT;
   if (pairs && (!positions || !inv_freq)) return Q3_ERR_ARGUMENT;
-  const long total = (long)num_tokens * H * ((n + 1) / 2);
+  if (pairing < 0 || pairing > 1 || (!pairing && x == out)) return Q3_ERR_ARGUMENT;  // halves read their partner: not in place
+  const long total = (long)num_tokens * H * (pairing ? (n + 1) / 2 : n);
   if (total == 0) return Q3_OK;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == Q3_DTYPE_F32)
     rotate_heads_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, xs_t, xs_h, (float*)out, os_t, os_h,
-                                                            positions, inv_freq, pairs, n, H, total);
+                                                            positions, inv_freq, pairs, n, H, total, pairing, magnitude);
   else if (dtype == Q3_DTYPE_BF16)
     rotate_heads_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, xs_t, xs_h, (bf16*)out, os_t, os_h,
-                                                           positions, inv_freq, pairs, n, H, total);
+                                                           positions, inv_freq, pairs, n, H, total, pairing, magnitude);
   else
     return Q3_ERR_ARGUMENT;
   return q3_launch_status();

@@ -288,6 +288,33 @@ Q3_EXPORT int q3_logit_scale_cap(float* logits, long total, float scale, float c
   return q3_launch_status();
 }
 
+// ---- x[r, i] *= sigmoid(g[r, i]): a gate on a sublayer's inner rows.  x dense [rows, n]; g rows g_stride
+//      elements apart (a slice of a wider product).  fp32 math, one rounding. ----
+template <typename T>
+__global__ void sigmoid_mul_kernel(T* __restrict__ x, const T* __restrict__ g, long g_stride, long total, int n) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long r = idx / n;
+  const int i = (int)(idx - r * n);
+  const float gate = to_f32(g[r * g_stride + i]);
+  x[idx] = from_f32<T>(to_f32(x[idx]) / (1.f + expf(-gate)));
+}
+
+Q3_EXPORT int q3_sigmoid_mul(int dtype, void* x, const void* g, long g_stride, int num_rows, int n,
+                             cudaStream_t stream) {
+  if (!x || !g || n < 1 || g_stride < n) return Q3_ERR_ARGUMENT;
+  const long total = (long)num_rows * n;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == Q3_DTYPE_F32)
+    sigmoid_mul_kernel<float><<<blocks, 256, 0, stream>>>((float*)x, (const float*)g, g_stride, total, n);
+  else if (dtype == Q3_DTYPE_BF16)
+    sigmoid_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)x, (const bf16*)g, g_stride, total, n);
+  else
+    return Q3_ERR_ARGUMENT;
+  return q3_launch_status();
+}
+
 // ---- RMSNorm of the sum, with what is pending normalised before it is added -----------------------
 // For blocks that norm a sublayer's output as well as its input:
 //   y   = pending[r]                                              (the sublayer's output, fp32 math)
@@ -297,6 +324,8 @@ Q3_EXPORT int q3_logit_scale_cap(float* logits, long total, float scale, float c
 // `add_ids/add_table` add embedding rows to the sum once more (a looped stack fed its input again);
 // `add_vec` (fp32 [H]) is added to every row's sum (a learned offset per pass of a loop).  Without `w`
 // nothing is normalised: out = v, rounded (the stream itself as the input of a product).
+// `center` bit 0: what is pending is layer-normed, (y - mean(y)) * rsqrt(mean((y - mean(y))^2) + post_eps) * post_w;
+// bit 1: so is the sum, out = (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps) * w.
 // One block per row; the row's y and v stay in shared memory between the passes.
 template <typename T>
 __global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int parts, long part_stride,
@@ -306,7 +335,7 @@ __global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int
                                        const T* __restrict__ add_table, const float* __restrict__ add_vec,
                                        const int* __restrict__ rows,
                                        const float* __restrict__ w, T* __restrict__ out, int H, float eps,
-                                       int write_resid, int vocab) {
+                                       int write_resid, int vocab, int center) {
   extern __shared__ float vals[];  // y[H], v[H], 33 for the reductions
   float* ys = vals;
   float* vs = vals + H;
@@ -315,12 +344,12 @@ __global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int
   pdl_launch_dependents();
   const int r = blockIdx.x;
   const long src = rows ? rows[r] : r;
-  float post_rstd = 1.f;
+  float post_rstd = 1.f, post_mean = 0.f;
   const bool pending = pending_any != nullptr;
   if (pending) {
     const T* prow = static_cast<const T*>(pending_any) + src * H;
     const float* frow = static_cast<const float*>(pending_any) + src * H;  // with parts: fp32 planes, added in order
-    float ss = 0.f;
+    float ss = 0.f, s1 = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float y;
       if (parts) {
@@ -331,8 +360,19 @@ __global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int
       }
       ys[i] = y;
       ss += y * y;
+      s1 += y;
     }
-    if (post_w) post_rstd = rsqrtf(block_sum(ss, red) / (float)H + post_eps);
+    if (post_w && (center & 1)) {  // layer norm: the mean first, then the mean of the squared deviations
+      post_mean = block_sum(s1, red) / (float)H;
+      float sd = 0.f;
+      for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = ys[i] - post_mean;
+        sd += d * d;
+      }
+      post_rstd = rsqrtf(block_sum(sd, red) / (float)H + post_eps);
+    } else if (post_w) {
+      post_rstd = rsqrtf(block_sum(ss, red) / (float)H + post_eps);
+    }
   }
   const T* trow = nullptr;
   if (ids) {
@@ -347,19 +387,31 @@ __global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int
     arow = add_table + (long)id * H;
   }
   float* rrow = resid ? resid + src * H : nullptr;
-  float ss = 0.f;
+  float ss = 0.f, s1 = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = trow ? to_f32(trow[i]) : rrow[i];
-    if (pending) v += post_w ? (ys[i] * post_rstd) * post_w[i] : ys[i];
+    if (pending) v += post_w ? ((ys[i] - post_mean) * post_rstd) * post_w[i] : ys[i];
     if (arow) v += to_f32(arow[i]);
     if (add_vec) v += add_vec[i];
     if (write_resid) rrow[i] = v;
     vs[i] = v;
     ss += v * v;
+    s1 += v;
   }
   T* orow = out + (long)r * H;
   if (!w) {  // the sum itself, rounded to the output's type
     for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>(vs[i]);
+    return;
+  }
+  if (center & 2) {
+    const float mean = block_sum(s1, red) / (float)H;
+    float sd = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float d = vs[i] - mean;
+      sd += d * d;
+    }
+    const float rstd = rsqrtf(block_sum(sd, red) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>(((vs[i] - mean) * rstd) * w[i]);
     return;
   }
   const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
@@ -375,7 +427,8 @@ __global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any,
                                            const T* __restrict__ table, const int* __restrict__ add_ids,
                                            const T* __restrict__ add_table, const float* __restrict__ add_vec,
                                            const int* __restrict__ rows, const float* __restrict__ w,
-                                           T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
+                                           T* __restrict__ out, int H, float eps, int write_resid, int vocab,
+                                           int center) {
   extern __shared__ __align__(16) float vals[];  // y[H], v[H], 33 for the reductions
   float* ys = vals;
   float* vs = vals + H;
@@ -384,12 +437,12 @@ __global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any,
   pdl_launch_dependents();
   const int r = blockIdx.x;
   const long src = rows ? rows[r] : r;
-  float post_rstd = 1.f;
+  float post_rstd = 1.f, post_mean = 0.f;
   const bool pending = pending_any != nullptr;
   if (pending) {
     const T* prow = static_cast<const T*>(pending_any) + src * H;
     const float* frow = static_cast<const float*>(pending_any) + src * H;
-    float ss = 0.f;
+    float ss = 0.f, s1 = 0.f;
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       float y[8];
       if (parts) {
@@ -405,9 +458,24 @@ __global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any,
       }
       store8(ys + i, y);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss += y[e] * y[e];
+      for (int e = 0; e < 8; ++e) {
+        ss += y[e] * y[e];
+        s1 += y[e];
+      }
     }
-    if (post_w) post_rstd = rsqrtf(block_sum(ss, red) / (float)H + post_eps);
+    if (post_w && (center & 1)) {  // layer norm: the mean first, then the mean of the squared deviations
+      post_mean = block_sum(s1, red) / (float)H;
+      float sd = 0.f;
+      for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+        float y[8];
+        load8(ys + i, y);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sd += (y[e] - post_mean) * (y[e] - post_mean);
+      }
+      post_rstd = rsqrtf(block_sum(sd, red) / (float)H + post_eps);
+    } else if (post_w) {
+      post_rstd = rsqrtf(block_sum(ss, red) / (float)H + post_eps);
+    }
   }
   const T* trow = nullptr;
   if (ids) {
@@ -423,7 +491,7 @@ __global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any,
   }
   float* rrow = resid ? resid + src * H : nullptr;
   T* orow = out + (long)r * H;
-  float ss = 0.f;
+  float ss = 0.f, s1 = 0.f;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float v[8], x[8];
     if (trow) load8(trow + i, v); else load8(rrow + i, v);
@@ -433,7 +501,7 @@ __global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any,
         float pw[8];
         load8(post_w + i, pw);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] += (x[e] * post_rstd) * pw[e];
+        for (int e = 0; e < 8; ++e) v[e] += ((x[e] - post_mean) * post_rstd) * pw[e];
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] += x[e];
@@ -456,16 +524,32 @@ __global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any,
     }
     store8(vs + i, v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    for (int e = 0; e < 8; ++e) {
+      ss += v[e] * v[e];
+      s1 += v[e];
+    }
   }
   if (!w) return;
-  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  float mean = 0.f, rstd;
+  if (center & 2) {
+    mean = block_sum(s1, red) / (float)H;
+    float sd = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float v[8];
+      load8(vs + i, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sd += (v[e] - mean) * (v[e] - mean);
+    }
+    rstd = rsqrtf(block_sum(sd, red) / (float)H + eps);
+  } else {
+    rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  }
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float v[8], wv[8];
     load8(vs + i, v);
     load8(w + i, wv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = (v[e] * rstd) * wv[e];
+    for (int e = 0; e < 8; ++e) v[e] = ((v[e] - mean) * rstd) * wv[e];
     store8(orow + i, v);
   }
 }
@@ -475,7 +559,7 @@ static int launch_fused_post_norm(const void* pending, int parts, long part_stri
                                   float* resid,
                                   const int* ids, const void* table, const int* add_ids, const void* add_table,
                                   const float* add_vec, const int* rows, const float* w, void* out, int num_rows,
-                                  int H, float eps, int write_resid, int vocab, cudaStream_t stream) {
+                                  int H, float eps, int write_resid, int vocab, int center, cudaStream_t stream) {
   if (num_rows == 0) return Q3_OK;
   const size_t smem = (size_t)(2 * H + 33) * sizeof(float);
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
@@ -489,7 +573,7 @@ static int launch_fused_post_norm(const void* pending, int parts, long part_stri
       cudaFuncSetAttribute(fused_post_norm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(fused_post_norm_vec_kernel<T>, dim3(num_rows), dim3(vthreads), smem, stream, pending, parts,
                       part_stride, post_w, post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, add_vec,
-                      rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
+                      rows, w, (T*)out, H, eps, write_resid, vocab, center) == cudaSuccess
                ? Q3_OK
                : Q3_ERR_LAUNCH;
   }
@@ -497,7 +581,7 @@ static int launch_fused_post_norm(const void* pending, int parts, long part_stri
   threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
   return launch_pdl(fused_post_norm_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, pending, parts, part_stride,
                     post_w, post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, add_vec, rows, w, (T*)out, H,
-                    eps, write_resid, vocab) == cudaSuccess
+                    eps, write_resid, vocab, center) == cudaSuccess
              ? Q3_OK
              : Q3_ERR_LAUNCH;
 }
@@ -508,8 +592,8 @@ Q3_EXPORT int q3_fused_post_norm(int dtype, const void* pending, int pending_par
                                  const float* post_w, float post_eps, float* resid,
                                  const int* ids, const void* table, const int* add_ids, const void* add_table,
                                  const float* add_vec, const int* rows, const float* w, void* out, int num_rows,
-                                 int H, float eps, int write_resid, int vocab, cudaStream_t stream) {
-  if (!out || H < 1) return Q3_ERR_ARGUMENT;
+                                 int H, float eps, int write_resid, int vocab, int center, cudaStream_t stream) {
+  if (!out || H < 1 || center < 0 || center > 3) return Q3_ERR_ARGUMENT;
   if (!ids && !resid) return Q3_ERR_ARGUMENT;
   if ((ids && !table) || (add_ids && !add_table)) return Q3_ERR_ARGUMENT;
   if (write_resid && !resid) return Q3_ERR_ARGUMENT;
@@ -517,10 +601,10 @@ Q3_EXPORT int q3_fused_post_norm(int dtype, const void* pending, int pending_par
   if (pending_parts < 0 || (pending_parts && (!pending || part_stride < 0))) return Q3_ERR_ARGUMENT;
   if (dtype == Q3_DTYPE_F32)
     return launch_fused_post_norm<float>(pending, pending_parts, part_stride, post_w, post_eps, resid, ids, table, add_ids, add_table, add_vec, rows,
-                                         w, out, num_rows, H, eps, write_resid, vocab, stream);
+                                         w, out, num_rows, H, eps, write_resid, vocab, center, stream);
   if (dtype == Q3_DTYPE_BF16)
     return launch_fused_post_norm<bf16>(pending, pending_parts, part_stride, post_w, post_eps, resid, ids, table, add_ids, add_table, add_vec, rows,
-                                        w, out, num_rows, H, eps, write_resid, vocab, stream);
+                                        w, out, num_rows, H, eps, write_resid, vocab, center, stream);
   return Q3_ERR_ARGUMENT;
 }
 

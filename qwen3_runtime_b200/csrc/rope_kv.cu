@@ -245,23 +245,32 @@ Q3_EXPORT int q3_rope_table(const float* inv_freq, float* cos_t, float* sin_t, i
   return q3_launch_status();
 }
 
-// ---- per-head q/k RMSNorm and cache write without a rotation, for rows whose k and v blocks start at
-// columns of their own and whose values have a size of their own ------------------------------------
+// ---- per-head q/k RMSNorm, optional rotation and cache write, for rows whose k and v blocks start at
+// columns of their own, whose values have a size and a head count of their own, and whose heads may be
+// made of several maps ------------------------------------------------------------------------------
 // One warp per (token, head).  q heads (columns h * D) are normalised in place; k heads (columns
-// k_start + g * D) are normalised into their page rows; v heads (columns v_start + g * Dv) are copied.
-// Key pages [pages, nkv, ps, D], value pages [pages, nkv, ps, Dv].  A weight of null leaves q (or k) as
-// it is.
+// k_start + g * D) are normalised into their page rows; v heads (columns v_start + g * Dv) are copied
+// (v_start may equal k_start: the values are then the keys as projected, since k is never changed in place).
+// Key pages [pages, nkv, ps, D], value pages [pages, nv, ps, Dv].  A weight of null leaves q (or k) as it is.
+// `maps`: a q or k head is `maps` consecutive parts of D / maps elements, each divided by its own root mean
+// square and multiplied by the one weight of D / maps elements.  `inv_freq` (fp32 [rot_half]): the first
+// 2 * rot_half elements of every part turn by angle = float(position) * inv_freq[i] (exact cosf/sinf, no
+// table, so no position is out of reach), pair i = (i, i + rot_half) with pairing 0 and (2i, 2i + 1) with
+// pairing 1; cos and sin are multiplied by `magnitude`.
 template <typename T, int WARPS>
-__global__ void qk_norm_store_kernel(T* __restrict__ proj, long row_stride, int nq, int nkv, int D, int Dv,
+__global__ void qk_norm_store_kernel(T* __restrict__ proj, long row_stride, int nq, int nkv, int nv, int D, int Dv,
                                      int k_start, int v_start, const float* __restrict__ q_w,
-                                     const float* __restrict__ k_w, float eps, const int* __restrict__ positions,
+                                     const float* __restrict__ k_w, float eps, int maps,
+                                     const float* __restrict__ inv_freq, int rot_half, int pairing, float magnitude,
+                                     const int* __restrict__ positions,
                                      const int* __restrict__ token_seq, const int* __restrict__ block_table,
                                      int max_pages, T* __restrict__ kpages, T* __restrict__ vpages, int ps,
                                      int num_tokens, int write_kv) {
+  extern __shared__ float stage[];  // WARPS * D
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads = write_kv ? nq + 2 * nkv : nq;
+  const int heads = write_kv ? nq + nkv + nv : nq;
   const long item = (long)blockIdx.x * WARPS + warp;
   if (item >= (long)num_tokens * heads) return;
   const int t = (int)(item / heads);
@@ -270,11 +279,12 @@ __global__ void qk_norm_store_kernel(T* __restrict__ proj, long row_stride, int 
   const int p = positions[t];
   long slot = 0;  // the token's row among all (page, head, place) rows
   if (hi >= nq) {
-    const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
+    const bool is_k = hi < nq + nkv;
+    const int kvh = is_k ? hi - nq : hi - nq - nkv;
     if (p < 0 || p / ps >= max_pages) return;  // no page in the table for this position: write nothing
     const int page = block_table[(long)token_seq[t] * max_pages + p / ps];
     if (page < 0) return;
-    slot = ((long)page * nkv + kvh) * ps + (p % ps);
+    slot = ((long)page * (is_k ? nkv : nv) + kvh) * ps + (p % ps);
   }
   if (hi >= nq + nkv) {  // value head: plain copy
     const T* x = row + v_start + (long)(hi - nq - nkv) * Dv;
@@ -285,39 +295,67 @@ __global__ void qk_norm_store_kernel(T* __restrict__ proj, long row_stride, int 
   T* x = hi < nq ? row + (long)hi * D : row + k_start + (long)(hi - nq) * D;
   T* dst = hi < nq ? x : kpages + slot * D;
   const float* w = hi < nq ? q_w : k_w;
-  if (!w) {
+  if (!w && !inv_freq) {
     if (dst != x)
       for (int d = lane; d < D; d += 32) dst[d] = x[d];
     return;
   }
-  float ss = 0.f;
-  for (int d = lane; d < D; d += 32) {
-    const float v = to_f32(x[d]);
-    ss += v * v;
+  float* xs = stage + warp * D;
+  for (int d = lane; d < D; d += 32) xs[d] = to_f32(x[d]);
+  __syncwarp();
+  const int Dm = D / maps;
+  if (w) {
+    for (int m = 0; m < maps; ++m) {
+      float ss = 0.f;
+      for (int d = lane; d < Dm; d += 32) ss += xs[m * Dm + d] * xs[m * Dm + d];
+      const float rstd = rsqrtf(warp_sum(ss) / (float)Dm + eps);
+      for (int d = lane; d < Dm; d += 32) xs[m * Dm + d] = (xs[m * Dm + d] * rstd) * w[d];
+    }
+    __syncwarp();
   }
-  const float rstd = rsqrtf(warp_sum(ss) / (float)D + eps);
-  for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>((to_f32(x[d]) * rstd) * w[d]);
+  for (int d = lane; d < D; d += 32) {
+    float y = xs[d];
+    const int dm = d % Dm;
+    if (inv_freq && dm < 2 * rot_half) {
+      const bool first = pairing ? (dm & 1) == 0 : dm < rot_half;  // the pair's first element
+      const int i = pairing ? dm >> 1 : (first ? dm : dm - rot_half);
+      const int pd = pairing ? dm ^ 1 : (first ? dm + rot_half : dm - rot_half);
+      const float ang = (float)p * inv_freq[i];
+      const float cs = cosf(ang) * magnitude, sn = sinf(ang) * magnitude;
+      const float yp = xs[d - dm + pd];
+      y = first ? y * cs - yp * sn : y * cs + yp * sn;
+    }
+    dst[d] = from_f32<T>(y);
+  }
 }
 
-Q3_EXPORT int q3_qk_norm_store(int dtype, void* proj, long row_stride, int nq, int nkv, int D, int Dv, int k_start,
-                               int v_start, const float* q_w, const float* k_w, float eps, const int* positions,
-                               const int* token_seq, const int* block_table, int max_pages, void* kpages,
-                               void* vpages, int ps, int num_tokens, int write_kv, cudaStream_t stream) {
-  if (!proj || !positions || nq < 1 || nkv < 1 || D < 1 || Dv < 1 || ps < 1) return Q3_ERR_ARGUMENT;
+Q3_EXPORT int q3_qk_norm_store(int dtype, void* proj, long row_stride, int nq, int nkv, int nv, int D, int Dv,
+                               int k_start, int v_start, const float* q_w, const float* k_w, float eps, int maps,
+                               const float* inv_freq, int rot_half, int pairing, float magnitude,
+                               const int* positions, const int* token_seq, const int* block_table, int max_pages,
+                               void* kpages, void* vpages, int ps, int num_tokens, int write_kv,
+                               cudaStream_t stream) {
+  if (!proj || !positions || nq < 1 || nkv < 1 || nv < 1 || D < 1 || Dv < 1 || ps < 1) return Q3_ERR_ARGUMENT;
+  if (maps < 1 || D % maps || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
+  if (inv_freq && (rot_half < 1 || 2 * rot_half > D / maps)) return Q3_ERR_ARGUMENT;
   if (write_kv && (!token_seq || !block_table || !kpages || !vpages || max_pages < 1)) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
   constexpr int WARPS = 4;
-  const long items = (long)num_tokens * (write_kv ? nq + 2 * nkv : nq);
+  const size_t smem = (size_t)WARPS * D * sizeof(float);
+  if (smem > 48 * 1024) return Q3_ERR_UNSUPPORTED;
+  const long items = (long)num_tokens * (write_kv ? nq + nkv + nv : nq);
   const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32)
-    e = launch_pdl(qk_norm_store_kernel<float, WARPS>, dim3(blocks), dim3(WARPS * 32), 0, stream, (float*)proj,
-                   row_stride, nq, nkv, D, Dv, k_start, v_start, q_w, k_w, eps, positions, token_seq, block_table,
-                   max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+    e = launch_pdl(qk_norm_store_kernel<float, WARPS>, dim3(blocks), dim3(WARPS * 32), smem, stream, (float*)proj,
+                   row_stride, nq, nkv, nv, D, Dv, k_start, v_start, q_w, k_w, eps, maps, inv_freq, rot_half, pairing,
+                   magnitude, positions, token_seq, block_table, max_pages, (float*)kpages, (float*)vpages, ps,
+                   num_tokens, write_kv);
   else if (dtype == Q3_DTYPE_BF16)
-    e = launch_pdl(qk_norm_store_kernel<bf16, WARPS>, dim3(blocks), dim3(WARPS * 32), 0, stream, (bf16*)proj,
-                   row_stride, nq, nkv, D, Dv, k_start, v_start, q_w, k_w, eps, positions, token_seq, block_table,
-                   max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+    e = launch_pdl(qk_norm_store_kernel<bf16, WARPS>, dim3(blocks), dim3(WARPS * 32), smem, stream, (bf16*)proj,
+                   row_stride, nq, nkv, nv, D, Dv, k_start, v_start, q_w, k_w, eps, maps, inv_freq, rot_half, pairing,
+                   magnitude, positions, token_seq, block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps,
+                   num_tokens, write_kv);
   else
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;

@@ -4,3 +4,4 @@ from . import qwen3  # noqa: F401  (first: the default architecture of a model-l
 from . import logesun  # noqa: F401
 from . import puladra  # noqa: F401
 from . import medilix  # noqa: F401
+from . import tabisun  # noqa: F401

@@ -56,7 +56,8 @@ _SIGNATURES = {
         "q3_add_bias": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "q3_logit_scale_cap": [c_void_p, c_long, c_float, c_float, c_void_p],
         "q3_fused_post_norm": [c_int, c_void_p, c_int, c_long, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+        "q3_sigmoid_mul": [c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p],
         "q3_gelu_gate_rows": [c_int, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_int,
                               c_void_p],
         "q3_relu_squared": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
@@ -75,9 +76,9 @@ _SIGNATURES = {
     "latent_attention": {
         "q3_latent_norm_rope_store": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                                       c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                                      c_int, c_void_p, c_void_p],
+                                      c_int, c_void_p, c_int, c_float, c_void_p],
         "q3_rotate_heads": [c_int, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p, c_int,
-                            c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_float, c_void_p],
         "q3_latent_attention": [c_int, c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_float, c_int,
                                 c_void_p],
@@ -115,14 +116,17 @@ _SIGNATURES = {
                                   c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "q3_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
-        "q3_qk_norm_store": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                             c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-                             c_void_p],
+        "q3_qk_norm_store": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                             c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                             c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "attention_generic": {
         "q3_paged_attention_generic": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                       c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p],
+                                       c_int, c_int, c_int, c_float, c_void_p, c_long, c_int, c_float, c_void_p],
+        "q3_paged_attention_diff": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                    c_float, c_float, c_float, c_void_p],
     },
     "linear_state": {
         "q3_decayed_state_scan": [c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long,
@@ -330,8 +334,10 @@ class CudaOps:
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
                    write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None,
-                   add_vector=None):
+                   add_vector=None, center=False, post_center=False):
         """RMSNorm of ``resid (+ pending)`` or of ``table[ids] (+ pending)``; see csrc/norm.cu.
+        ``center`` / ``post_center``: the sum's norm / the pending output's norm is a layer norm with a
+        weight and no bias (the mean is taken off and the variance is the mean squared deviation).
         ``pending`` is ``[rows, H]`` of the output's type, or fp32 ``[parts, rows, H]``: the
         partial sums of a product (:meth:`linear` with ``partial_sums``), added in order.
         ``post_weight`` / ``post_eps``: what is pending is RMS-normalised with this weight before it
@@ -344,7 +350,8 @@ class CudaOps:
         if add_vector is not None and (add_vector.dtype != torch.float32 or add_vector.numel() != H
                                        or not add_vector.is_contiguous()):
             raise KernelError("fused_norm: add_vector is a dense float32 vector of the rows' width")
-        if post_weight is not None or add_ids is not None or add_vector is not None or weight is None:
+        if (post_weight is not None or add_ids is not None or add_vector is not None or weight is None
+                or center or post_center):
             pparts = pstride = 0
             if pending is not None and pending.dim() == 3:
                 if pending.dtype != torch.float32 or pending.stride(2) != 1 or pending.stride(1) != H:
@@ -362,7 +369,7 @@ class CudaOps:
             self._call("norm", "q3_fused_post_norm", "fused_post_norm", _dtype_code(out.dtype), _ptr(pending),
                        pparts, pstride, _ptr(post_weight), float(post_eps), _ptr(resid), _ptr(ids), _ptr(table), _ptr(add_ids),
                        _ptr(add_table), _ptr(add_vector), _ptr(rows), _ptr(weight), _ptr(out), n, H, float(eps),
-                       int(bool(write_resid)), vocab)
+                       int(bool(write_resid)), vocab, int(bool(post_center)) | (int(bool(center)) << 1))
             return out
         parts = stride = 0
         if pending is not None and pending.dim() == 3:
@@ -495,6 +502,18 @@ class CudaOps:
         self._call("norm", "q3_silu_mul", "silu_mul",
                    _dtype_code(out.dtype), _ptr(gate_up), _ptr(out), out.shape[0], I)
         return out
+
+    def sigmoid_mul(self, x, gate):
+        """``x *= sigmoid(gate)`` in place: ``x`` dense ``[rows, n]``, ``gate`` ``[rows, n]`` (a slice of wider
+        rows will do); float32 math, one rounding."""
+        rows, n = x.shape
+        if not x.is_contiguous() or gate.shape != x.shape or gate.stride(1) != 1 or gate.dtype != x.dtype:
+            raise KernelError("sigmoid_mul: dense rows and a gate of their shape and type with unit stride")
+        if self.timing is not None:
+            self._costs(3 * rows * n * x.element_size())
+        self._call("norm", "q3_sigmoid_mul", "sigmoid_mul", _dtype_code(x.dtype), _ptr(x), _ptr(gate), gate.stride(0),
+                   rows, n)
+        return x
 
     def clamped_glu(self, gate_up, out, *, limit, alpha, up_offset):
         """``out = g * sigmoid(alpha g) * (u + up_offset)`` with ``g = min(gate, limit)`` and
@@ -659,13 +678,16 @@ class CudaOps:
 
     # ---- attention through a latent (csrc/latent_attention.cu, csrc/head_gemm.cu) ---------------
     def latent_norm_rope_store(self, down, *, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, inv_freq, positions,
-                               token_seq, block_table, pages, page_size, write, q_out):
+                               token_seq, block_table, pages, page_size, write, q_out, pairing="interleaved",
+                               magnitude=1.0):
         """Rows of ``down`` are ``[query latent | key latent | shared key part]``: the query latent is
         RMS-normalised into ``q_out``; the key latent is RMS-normalised, the key part rotated
-        (interleaved pairs, angle ``position * inv_freq[i]``), and both are written into the token's
-        row of ``pages`` ``[pages, page_size, kv_rank + rot_dim]``."""
+        (angle ``position * inv_freq[i]``, pairs as ``pairing`` says, cos and sin times ``magnitude``),
+        and both are written into the token's row of ``pages`` ``[pages, page_size, kv_rank + rot_dim]``.
+        ``q_rank`` 0: no query latent (``q_weight`` and ``q_out`` None); ``down`` may be a slice of wider rows."""
         T = down.shape[0]
-        if down.stride(1) != 1 or down.shape[1] != q_rank + kv_rank + rot_dim or not q_out.is_contiguous():
+        if (down.stride(1) != 1 or down.shape[1] != q_rank + kv_rank + rot_dim
+                or (q_out is not None and not q_out.is_contiguous()) or (q_rank > 0) != (q_out is not None)):
             raise KernelError("latent_norm_rope_store: rows of q_rank + kv_rank + rot_dim elements")
         if pages is not None and (pages.shape[-1] != kv_rank + rot_dim or not pages.is_contiguous()):
             raise KernelError("latent_norm_rope_store: pages are dense [pages, page_size, kv_rank + rot_dim]")
@@ -676,7 +698,7 @@ class CudaOps:
                    _dtype_code(down.dtype), _ptr(down), down.stride(0), q_rank, kv_rank, rot_dim, _ptr(q_weight),
                    _ptr(kv_weight), float(eps), _ptr(inv_freq), pairs, _ptr(positions), _ptr(token_seq),
                    _ptr(block_table), block_table.shape[1] if block_table is not None else 0, _ptr(pages),
-                   page_size, T, int(bool(write)), _ptr(q_out))
+                   page_size, T, int(bool(write)), _ptr(q_out), self.PAIRINGS[pairing], float(magnitude))
 
     @staticmethod
     def _head_strides(x, what):
@@ -684,14 +706,16 @@ class CudaOps:
             raise KernelError(f"{what}: [tokens, heads, n] with unit stride along n")
         return x.stride(0), x.stride(1)
 
-    def rotate_heads(self, x, out, *, positions, inv_freq):
-        """``out[t, h] = rotate(x[t, h])`` by the token's position (interleaved pairs; elements beyond
-        ``2 * len(inv_freq)`` are copied).  ``x`` and ``out`` may be slices of wider rows."""
+    def rotate_heads(self, x, out, *, positions, inv_freq, pairing="interleaved", magnitude=1.0):
+        """``out[t, h] = rotate(x[t, h])`` by the token's position (pairs as ``pairing`` says, cos and sin
+        times ``magnitude``; elements beyond ``2 * len(inv_freq)`` are copied).  ``x`` and ``out`` may be
+        slices of wider rows (with the halves pairing not the same ones)."""
         T, H, n = x.shape
         xs, os_ = self._head_strides(x, "rotate_heads"), self._head_strides(out, "rotate_heads")
         pairs = inv_freq.numel() if inv_freq is not None else 0
         self._call("latent_attention", "q3_rotate_heads", "rotate_heads", _dtype_code(x.dtype), _ptr(x), xs[0], xs[1],
-                   _ptr(out), os_[0], os_[1], _ptr(positions), _ptr(inv_freq), pairs, n, H, T)
+                   _ptr(out), os_[0], os_[1], _ptr(positions), _ptr(inv_freq), pairs, n, H, T,
+                   self.PAIRINGS[pairing], float(magnitude))
         return out
 
     def head_linear(self, x, weight, out):
@@ -921,27 +945,45 @@ class CudaOps:
                   page_size, T, int(bool(write_kv)), self.PAIRINGS[pairing], _ptr(self._error_word(qkv.device)))
 
     def qk_norm_store(self, proj, *, num_heads, num_kv_heads, head_dim, value_dim, k_start, v_start, q_weight,
-                      k_weight, eps, positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
-        """Per-head q/k RMSNorm (weights float32 ``[head_dim]`` shared by the heads, or None: as they are) without
-        a rotation, and the write of k and v into their pages (csrc/rope_kv.cu).  A row of ``proj`` holds the
+                      k_weight, eps, positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv,
+                      maps=1, num_value_heads=None, inv_freq=None, pairing="half", magnitude=1.0):
+        """Per-head q/k RMSNorm (weights float32 shared by the heads, or None: as they are), an optional
+        rotation, and the write of k and v into their pages (csrc/rope_kv.cu).  A row of ``proj`` holds the
         query heads from column 0, the key heads from ``k_start`` and the value heads (``value_dim`` each) from
-        ``v_start``; q is normalised in place."""
+        ``v_start`` (which may be ``k_start``: the values are the keys as projected); q is changed in place.
+        ``maps``: a head is that many consecutive parts of ``head_dim / maps`` elements, each normalised by
+        itself with the one weight of that size.  ``num_value_heads``: the values' head count when it is not the
+        keys'.  ``inv_freq`` (float32 ``[pairs]``): the first ``2 * pairs`` elements of every part turn by
+        ``position * inv_freq[i]``, pairs as ``pairing`` says, cos and sin times ``magnitude``; no table."""
         T = proj.shape[0]
         if proj.stride(1) != 1:
             raise KernelError("qk_norm_store: unit-stride rows")
+        maps = int(maps)
+        if maps < 1 or head_dim % maps:
+            raise KernelError(f"qk_norm_store: a head of {head_dim} does not split into {maps} maps")
+        for w in (q_weight, k_weight):
+            if w is not None and (w.dtype != torch.float32 or w.numel() != head_dim // maps):
+                raise KernelError("qk_norm_store: weights are float32 vectors of one map's size")
+        nv = int(num_value_heads or num_kv_heads)
+        pairs = inv_freq.numel() if inv_freq is not None else 0
+        if inv_freq is not None and (inv_freq.dtype != torch.float32 or 2 * pairs > head_dim // maps):
+            raise KernelError("qk_norm_store: float32 inverse frequencies, at most half a map's size of them")
         max_pages = block_table.shape[1] if block_table is not None else 0
         if self.timing is not None:
             self._costs(2 * T * ((num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim) * proj.element_size())
         self._call("rope_kv", "q3_qk_norm_store", "qk_norm_store", _dtype_code(proj.dtype), _ptr(proj), proj.stride(0),
-                   num_heads, num_kv_heads, head_dim, value_dim, int(k_start), int(v_start), _ptr(q_weight),
-                   _ptr(k_weight), float(eps), _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages,
+                   num_heads, num_kv_heads, nv, head_dim, value_dim, int(k_start), int(v_start), _ptr(q_weight),
+                   _ptr(k_weight), float(eps), maps, _ptr(inv_freq), pairs, self.PAIRINGS[pairing], float(magnitude),
+                   _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages,
                    _ptr(k_pages), _ptr(v_pages), page_size, T, int(bool(write_kv)))
 
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
                         token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None,
-                        value_dim=None, keep_first=0, sink=None, gate=None):
-        """Causal attention of every token of the step over its sequence's pages.  ``value_dim``:
+                        value_dim=None, keep_first=0, sink=None, gate=None, chunk=None, softcap=None):
+        """Causal attention of every token of the step over its sequence's pages.  ``chunk``: position p sees
+        keys from ``floor(p / chunk) * chunk`` on only.  ``softcap``: scores become ``softcap * tanh(score /
+        softcap)`` after the scale.  ``value_dim``:
         values have a size of their own (``v_pages`` ``[pages, kv heads, page, value_dim]``); ``out`` may
         then be a view of wider rows, head h at column ``h * value_dim``.  ``keep_first``: with a window, the
         sequence's first tokens stay visible as well.  ``sink``: a score without a value that is added to the
@@ -954,6 +996,9 @@ class CudaOps:
         keep_first = int(keep_first or 0) if window else 0
         plain = not keep_first and sink is None and gate is None  # what the tcgen05 kernel takes
         dense = out.stride(0) == num_heads * Dv and Dv == head_dim
+        chunk, softcap = int(chunk or 0), float(softcap or 0.0)
+        if chunk or softcap:
+            dense = False  # the specialised kernels know neither: the general kernel
         extras = dict(keep_first=keep_first, sink=sink, gate=gate)
         if gate is not None and (gate.stride(1) != 1 or gate.shape != (T, num_heads * Dv) or gate.dtype != out.dtype):
             raise KernelError("paged_attention: the gate is [tokens, heads * value_dim] of the output's type")
@@ -1022,7 +1067,29 @@ class CudaOps:
                    _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                   block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads,
                   num_kv_heads, head_dim, Dv, page_size, float(scale), int(window or 0), int(keep_first or 0),
-                  int(sink is not None), float(sink or 0.0), _ptr(gate), gate.stride(0) if gate is not None else 0)
+                  int(sink is not None), float(sink or 0.0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                  chunk, softcap)
+        return out
+
+    def differential_attention(self, q, q_stride, *, num_heads, num_kv_heads, map_dim, value_dim, k_pages, v_pages,
+                               block_table, token_seq, positions, out, page_size, scale, lam, eps, out_scale,
+                               window=None, chunk=None, step=None):
+        """Two softmax maps per head over the same values (csrc/attention_generic.cu): a query head is
+        ``[q1 | q2]`` of ``map_dim`` each at column ``h * 2 * map_dim``, ``k_pages`` ``[pages, kv heads, page,
+        2 * map_dim]`` hold ``[k1 | k2]``, ``v_pages`` ``[pages, kv heads, page, value_dim]``.  ``out[t, h] =
+        (a1 - lam * a2)`` divided by its root mean square (``eps`` inside the root), times ``out_scale``."""
+        T = out.shape[0]
+        if map_dim > 256 or value_dim > 256 or out.stride(1) != 1:
+            raise KernelError("differential_attention: map and value sizes up to 256, unit stride")
+        if k_pages.shape[-1] != 2 * map_dim or v_pages.shape[-1] != value_dim:
+            raise KernelError("differential_attention: key pages hold both maps, value pages the values")
+        if self.timing is not None and step is not None:
+            self._costs(*self._attention_cost(step, num_heads, num_kv_heads, map_dim + value_dim // 2, out))
+        self._call("attention_generic", "q3_paged_attention_diff", "differential_attention", _dtype_code(out.dtype),
+                   _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                   _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads, num_kv_heads, map_dim,
+                   value_dim, page_size, float(scale), int(window or 0), int(chunk or 0), float(lam), float(eps),
+                   float(out_scale))
         return out
 
     @staticmethod

@@ -1,6 +1,6 @@
 # importing the modules registers the built-in parts
-from . import (attention, block, conv_attention, embedding, experts, feed_forward, gated_memory,  # noqa: F401
-               latent_attention, linear_state, norm, position, sink_attention, token_side)
+from . import (attention, block, conv_attention, differential_attention, embedding, experts,  # noqa: F401
+               feed_forward, gated_memory, latent_attention, linear_state, norm, position, sink_attention, token_side)
 from .base import (
     BuildContext,
     ParamSpec,

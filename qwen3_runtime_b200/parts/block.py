@@ -5,7 +5,9 @@ after the sublayers.
 ``sandwich_norm``: a norm before and after each sublayer, x += norm_b(mixer(norm(x))) and
 x += norm_b(ff(norm(x))), the feed-forward being optional.
 ``parallel_norms``: mixer and feed-forward read the same stream through a norm each and are added
-together, x += mixer(norm_a(x)) + ff(norm_b(x)); the feed-forward is optional."""
+together, x += mixer(norm_a(x)) + ff(norm_b(x)); the feed-forward is optional.
+``output_norm``: the sublayers read the stream itself and only their outputs are normed,
+x += norm_a(mixer(x)); x += norm_b(ff(x)); the feed-forward is optional."""
 
 from __future__ import annotations
 
@@ -215,6 +217,69 @@ class ParallelNormsBlock(Part):
         stream.pending_more = self.feed_forward.forward(h_ff, step)
 
 
+class OutputNormBlock(Part):
+    """x += norm_a(mixer(x)); x += norm_b(ff(x)): no norm on a sublayer's input.  The output norms run no
+    kernel of their own: a sublayer's output is left on the stream with its norm, and whichever kernel reads
+    the stream next (this block's fold before the feed-forward, the next block's before its mixer, the model's
+    final norm) normalises it, adds it to the float32 sum and hands on the sum, rounded to the activation type
+    (or its norm), in one pass.  ``feed_forward`` may be None."""
+
+    category = "block"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.mixer = build_part("mixer", spec["mixer"], ctx)
+        self.mixer_out_norm = build_part("norm", spec["mixer_out_norm"], ctx)
+        self.children = {spec.get("mixer_prefix", "mixer."): self.mixer,
+                         spec.get("mixer_out_norm_prefix", "mixer_out_norm."): self.mixer_out_norm}
+        self.feed_forward = self.feed_forward_out_norm = None
+        if spec.get("feed_forward") is not None:
+            self.feed_forward = build_part("feed_forward", spec["feed_forward"], ctx)
+            self.feed_forward_out_norm = build_part("norm", spec["feed_forward_out_norm"], ctx)
+            self.children.update({
+                spec.get("feed_forward_prefix", "feed_forward."): self.feed_forward,
+                spec.get("feed_forward_out_norm_prefix", "feed_forward_out_norm."): self.feed_forward_out_norm})
+        self.entry_norm = self.mixer_out_norm  # the part whose kernel reads the stream first
+        self._owners = {prefix + name: (part, name) for prefix, part in self.children.items()
+                        for name in part.param_specs()}
+
+    def exit_to(self, norms) -> None:
+        """A sublayer's output is normalised before it is added, so it is never taken as partial sums."""
+
+    def param_specs(self):
+        return {full: part.param_specs()[name] for full, (part, name) in self._owners.items()}
+
+    def load(self, tensors):
+        per_part: dict[int, dict] = {}
+        for full, (part, name) in self._owners.items():
+            per_part.setdefault(id(part), {})[name] = tensors[full]
+        for part in self.children.values():
+            part.load(per_part.get(id(part), {}))
+
+    def kernel_groups(self):
+        return ["norm", *[g for part in self.children.values() for g in part.kernel_groups()]]
+
+    def step_choosers(self):
+        return {name: fn for part in self.children.values() for name, fn in part.step_choosers().items()}
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def position_limit(self):
+        limits = [n for n in (part.position_limit() for part in self.children.values()) if n is not None]
+        return min(limits) if limits else None
+
+    def forward(self, stream: ResidualStream, step: StepContext, cache) -> None:
+        h = self.mixer_out_norm.add_norm(stream, normalise=False)  # the stream itself
+        stream.pending = self.mixer.forward(h, step, cache)
+        stream.pending_norm = self.mixer_out_norm.pending_scale()
+        if self.feed_forward is not None:
+            h = self.feed_forward_out_norm.add_norm(stream, normalise=False)
+            stream.pending = self.feed_forward.forward(h, step)
+            stream.pending_norm = self.feed_forward_out_norm.pending_scale()
+
+
+register_part("block", "output_norm", OutputNormBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "parallel_norms", ParallelNormsBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)

@@ -56,7 +56,7 @@ class DecoderModel:
         for name, shape, kind in s.shared_tables:
             out[name] = ParamSpec(tuple(shape), kind)
         for i, block in enumerate(self.blocks):
-            prefix = s.block_prefix.format(index=i)
+            prefix = s.prefix_of(i)
             for name, ps in block.param_specs().items():
                 out[prefix + name] = ps
         for name, ps in self.final_norm.param_specs().items():
@@ -87,7 +87,7 @@ class DecoderModel:
         for name, _shape, _kind in s.shared_tables:  # before the blocks: their parts may read them
             self.ctx.shared[name] = fetch(name).contiguous()
         for i, block in enumerate(self.blocks):
-            prefix = s.block_prefix.format(index=i)
+            prefix = s.prefix_of(i)
             block.load({name: fetch(prefix + name) for name in block.param_specs()})
         self.final_norm.load({name: fetch(s.final_norm_prefix + name) for name in self.final_norm.param_specs()})
         self.head = self.embed if s.tie_word_embeddings else fetch(s.head_name).contiguous()

@@ -2,7 +2,9 @@
 (qwen3_runtime/layers/ops.py:17-20; residual form :28-37).  ``weight_offset``: the stored weight
 is the deviation from this value, which is added to it when it is loaded (y = ... * (offset + w)).
 ``groups`` > 1: a row is cut into that many equal consecutive parts and each is divided by its own root
-mean square (the weight still spans the whole row)."""
+mean square (the weight still spans the whole row).
+``layernorm``: y = (x - mean(x)) * rsqrt(mean((x - mean(x))^2) + eps) * w, a weight and no bias; the same part
+with the mean taken off first (the same kernels with their ``center`` flags)."""
 
 from __future__ import annotations
 
@@ -14,6 +16,7 @@ from .base import BuildContext, ParamSpec, Part, ResidualStream, register_part
 class RMSNorm(Part):
     category = "norm"
     adds_partial_sums = True
+    center = False  # True: a layer norm (the mean is taken off before the mean square)
 
     def __init__(self, spec, ctx: BuildContext):
         super().__init__(spec, ctx)
@@ -25,6 +28,8 @@ class RMSNorm(Part):
         self.groups = int(spec.get("groups") or 1)
         if self.groups < 1 or self.size % self.groups:
             raise ValueError(f"rmsnorm: {self.size} elements do not split into {self.groups} equal groups")
+        if self.center and self.groups > 1:
+            raise ValueError("layernorm: no groups")
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
@@ -35,9 +40,10 @@ class RMSNorm(Part):
         if self.weight_offset:
             self.weight = (self.weight.float() + self.weight_offset).contiguous()
 
-    def pending_scale(self) -> tuple[torch.Tensor, float]:
-        """This norm as something the next norm applies to what is pending (``ResidualStream.pending_norm``)."""
-        return self.weight, self.eps
+    def pending_scale(self) -> tuple:
+        """This norm as something the next norm applies to what is pending (``ResidualStream.pending_norm``):
+        ``(weight, eps)``, or ``(weight, eps, True)`` for a layer norm."""
+        return (self.weight, self.eps, True) if self.center else (self.weight, self.eps)
 
     def kernel_groups(self):
         return ["norm"]
@@ -53,12 +59,18 @@ class RMSNorm(Part):
         ``(this norm's rows, the second norm's rows)`` of the same sum, made by one kernel."""
         n = stream.num_tokens if rows is None else (num_rows if num_rows is not None else rows.numel())
         if self.groups > 1 or second is not None or stream.pending_more is not None:
+            if self.center:
+                raise NotImplementedError("layernorm: one norm of one pending output at a time")
             return self._grouped(stream, rows, n, normalise, second)
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=self.ctx.device)
         keep = rows is None
         extra = {}
         if stream.pending is not None and stream.pending_norm is not None:
             extra.update(post_weight=stream.pending_norm[0], post_eps=stream.pending_norm[1])
+            if len(stream.pending_norm) > 2 and stream.pending_norm[2]:
+                extra.update(post_center=True)
+        if self.center and normalise:
+            extra.update(center=True)
         if stream.add_source:
             if stream.embed is not None:
                 raise ValueError("the embedding cannot be added again before it was read once")
@@ -116,4 +128,9 @@ def fold_stream(ops, stream: ResidualStream, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class LayerNorm(RMSNorm):
+    center = True
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

@@ -7,9 +7,13 @@ sink in the softmax and a gate on the heads' outputs.
     p_j = exp(s_j) / (exp(sink) + sum_j' exp(s_j'))      (``sink`` None: a plain softmax)
     out = W_o (heads' outputs * sigmoid(g))              (``gate`` None: no gate)
 
-Positions do not enter the scores.  Keys and values may have unlike sizes per head.  The cache is a
-paged key/value layer whose group gives back the pages that lie wholly between the kept first tokens
-and the window.
+Keys and values may have unlike sizes per head.  The cache is a paged key/value layer whose group gives
+back the pages that lie wholly between the kept first tokens and the window.  Further options:
+``position`` (a rotary position part with inverse frequencies: q and k are turned after their norm, inside
+the same kernel; without it positions do not enter the scores); ``softcap`` (scores become softcap *
+tanh(score / softcap) after the scale); ``values="keys"`` (there is no W_v: the values are the keys as
+projected, before norm and rotation); ``chunk`` (position i sees j <= i of its own chunk only, chunks of
+that many tokens counted from the sequence's first token).
 """
 
 from __future__ import annotations
@@ -17,7 +21,8 @@ from __future__ import annotations
 import torch
 
 from ..cache.layout import KVLayerSpec
-from .base import BuildContext, ParamSpec, Part, StepContext, register_part
+from ..config.spec import PartSpec
+from .base import BuildContext, ParamSpec, Part, StepContext, build_part, register_part
 from .linear_state import _pad_rows
 
 
@@ -43,6 +48,22 @@ class SinkWindowAttention(Part):
             raise ValueError(f"dim={self.dim}, vdim={self.vdim}: the attention kernels take sizes up to 256")
         if self.gate not in (None, "sigmoid"):
             raise ValueError(f"sink_window_attention: gate is 'sigmoid' or absent, not {self.gate!r}")
+        self.softcap = float(spec.get("softcap") or 0.0) or None
+        self.chunk = int(spec.get("chunk") or 0) or None
+        self.values_are_keys = spec.get("values", "own") == "keys"
+        if spec.get("values", "own") not in ("own", "keys"):
+            raise ValueError(f"sink_window_attention: values are 'own' or 'keys', not {spec.get('values')!r}")
+        if self.values_are_keys and self.vdim != self.dim:
+            raise ValueError("sink_window_attention: values that are the keys have the keys' size")
+        if self.chunk and self.window:
+            raise ValueError("sink_window_attention: a window or chunks, not both")
+        self.position = build_part("position", spec.get("position") or PartSpec("none"), ctx)
+        if self.position.style == "rotary":
+            if not hasattr(self.position, "inverse_frequencies") or self.position.rotary_dim > self.dim:
+                raise ValueError("sink_window_attention turns q and k by angles worked out from inverse "
+                                 "frequencies over at most the head's size; the position part offers otherwise")
+        elif self.position.style != "none":
+            raise ValueError(f"sink_window_attention has no {self.position.style!r} position encoding")
         self.in_weight = self.o_weight = self.q_norm = self.k_norm = None
         self.starts: list[int] = []
 
@@ -50,6 +71,8 @@ class SinkWindowAttention(Part):
         H, G, D, Dv, W = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.hidden_size
         specs = {"q": ParamSpec((H * D, W)), "k": ParamSpec((G * D, W)), "v": ParamSpec((G * Dv, W)),
                  "o": ParamSpec((W, H * Dv))}
+        if self.values_are_keys:
+            del specs["v"]
         if self.gate:
             specs["g"] = ParamSpec((H * Dv, W))
         if self.qk_norm_eps is not None:
@@ -58,8 +81,12 @@ class SinkWindowAttention(Part):
         return specs
 
     def load(self, tensors):
-        blocks = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.gate else [])
-        self.in_weight, self.starts = _pad_rows(blocks)
+        if self.values_are_keys:  # no W_v: the value heads are read where the key heads are
+            self.in_weight, starts = _pad_rows([tensors["q"], tensors["k"]] + ([tensors["g"]] if self.gate else []))
+            self.starts = [starts[0], starts[1], starts[1], *starts[2:]]
+        else:
+            blocks = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.gate else [])
+            self.in_weight, self.starts = _pad_rows(blocks)
         self.o_weight = tensors["o"].contiguous()
         self.q_norm = tensors.get("q.norm")
         self.k_norm = tensors.get("k.norm")
@@ -76,7 +103,7 @@ class SinkWindowAttention(Part):
         kernel (64, 128) take (ops.paged_attention sends a dense output there), with the window's kept first tokens, the
         sink and the gate."""
         return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128, 256)
-                and self.num_heads // self.num_kv_heads <= 16)
+                and self.num_heads // self.num_kv_heads <= 16 and not self.softcap and not self.chunk)
 
     def _slices_key(self):
         reach = self.window + self.keep_first if self.window else None  # the most keys a token sees
@@ -91,7 +118,11 @@ class SinkWindowAttention(Part):
         return {key: lambda kv_lens: model(kv_lens, key[1], key[2], key[3])}
 
     def cache_spec(self):
-        return KVLayerSpec(self.num_kv_heads, self.dim, self.window, value_dim=self.vdim, keep_first=self.keep_first)
+        return KVLayerSpec(self.num_kv_heads, self.dim, self.window, value_dim=self.vdim, keep_first=self.keep_first,
+                           chunk=self.chunk)
+
+    def position_limit(self):
+        return self.position.position_limit()
 
     def forward(self, h: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
         ops = self.ops
@@ -102,7 +133,9 @@ class SinkWindowAttention(Part):
         ctx = torch.empty((h.shape[0], H * Dv), dtype=h.dtype, device=h.device)
         gate = proj[:, s[3]:s[3] + H * Dv] if self.gate else None
         fusable = getattr(ops, "decode_new_token_ok", None)
-        if (fusable is not None and step.decode_only and cache.writes and self._specialised()
+        rotary = self.position.style == "rotary"
+        if (fusable is not None and step.decode_only and cache.writes and self._specialised() and not rotary
+                and not self.values_are_keys
                 and s[1] == H * D and s[2] == (H + G) * D  # q, k and v heads side by side, as that kernel reads them
                 and fusable(proj, num_heads=H, num_kv_heads=G, head_dim=D, cos=None, q_weight=self.q_norm,
                             k_weight=self.k_norm)):
@@ -122,12 +155,15 @@ class SinkWindowAttention(Part):
                           q_weight=self.q_norm, k_weight=self.k_norm,
                           eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, positions=step.positions,
                           token_seq=step.token_seq, block_table=block_table, k_pages=cache.k_pages,
-                          v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes)
+                          v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes,
+                          **(dict(inv_freq=self.position.inverse_frequencies(), pairing=self.position.pairing,
+                                  magnitude=getattr(self.position, "magnitude", 1.0)) if rotary else {}))
         ops.paged_attention(proj, proj.stride(0), num_heads=H, num_kv_heads=G, head_dim=D, k_pages=cache.k_pages,
                             v_pages=cache.v_pages, block_table=block_table, token_seq=step.token_seq,
                             positions=step.positions, out=ctx, page_size=cache.page_size, scale=self.scale,
                             window=self.window, step=step, value_dim=Dv, keep_first=self.keep_first, sink=self.sink,
-                            gate=gate, decode_slices=step.choices.get(self._slices_key()))
+                            gate=gate, decode_slices=step.choices.get(self._slices_key()),
+                            **(dict(chunk=self.chunk, softcap=self.softcap) if self.chunk or self.softcap else {}))
         return ops.linear(ctx, self.o_weight)
 
 

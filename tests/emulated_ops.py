@@ -21,7 +21,7 @@ class TorchOps:
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
                    write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None,
-                   add_vector=None):
+                   add_vector=None, center=False, post_center=False):
         n = out.shape[0] if num_rows is None else num_rows
         src = rows[:n].long() if rows is not None else torch.arange(n, device=out.device)
         if ids is not None:
@@ -36,6 +36,8 @@ class TorchOps:
             total = pending[src].float()
         if pending is not None:
             if post_weight is not None:  # what is pending is normalised before it is added
+                if post_center:
+                    total = total - total.mean(-1, keepdim=True)
                 total = (total * torch.rsqrt(total.pow(2).mean(-1, keepdim=True) + post_eps)) * post_weight.float()
             v = v + total
         if add_ids is not None:
@@ -47,9 +49,15 @@ class TorchOps:
         if weight is None:  # the sum itself, rounded
             out[:n] = v.to(out.dtype)
             return out
+        if center:
+            v = v - v.mean(-1, keepdim=True)
         var = v.pow(2).mean(-1, keepdim=True)
         out[:n] = ((v * torch.rsqrt(var + eps)) * weight.float()).to(out.dtype)
         return out
+
+    def sigmoid_mul(self, x, gate):
+        x.copy_((x.float() * torch.sigmoid(gate.float())).to(x.dtype))
+        return x
 
     def grouped_norm(self, out, weight, eps, groups, *, resid, pending=None, pending_more=None, rows=None,
                      write_resid=True, num_rows=None, out2=None, weight2=None):
@@ -139,28 +147,56 @@ class TorchOps:
         return decay, k_scale, m_run
 
     def qk_norm_store(self, proj, *, num_heads, num_kv_heads, head_dim, value_dim, k_start, v_start, q_weight, k_weight,
-                      eps, positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+                      eps, positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv, maps=1,
+                      num_value_heads=None, inv_freq=None, pairing="half", magnitude=1.0):
         T = proj.shape[0]
         H, G, D, Dv = num_heads, num_kv_heads, head_dim, value_dim
+        Gv = int(num_value_heads or G)
+        Dm = D // maps
 
-        def unit(x, w):
-            if w is None:
-                return x
-            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        def unit(x, w):  # x [T, n, D] float: every map normalised by itself, then turned
+            x = x.reshape(T, -1, maps, Dm)
+            if w is not None:
+                x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+            if inv_freq is not None:
+                x = self._turn_pairs(x, positions.long(), inv_freq, pairing, magnitude)
+            return x.reshape(T, -1, D)
 
+        raw_k = proj[:, k_start:k_start + G * D].reshape(T, G, D).float()
+        raw_v = proj[:, v_start:v_start + Gv * Dv].reshape(T, Gv, Dv).clone()
         q = unit(proj[:, : H * D].reshape(T, H, D).float(), q_weight)
         proj[:, : H * D] = q.reshape(T, H * D).to(proj.dtype)
         if not write_kv:
             return
-        k = unit(proj[:, k_start:k_start + G * D].reshape(T, G, D).float(), k_weight).to(proj.dtype)
-        v = proj[:, v_start:v_start + G * Dv].reshape(T, G, Dv)
+        k = unit(raw_k, k_weight).to(proj.dtype)
         for t in range(T):
             p = int(positions[t])
             page = int(block_table[int(token_seq[t]), p // page_size])
             if page < 0:
                 continue
             k_pages[page, :, p % page_size, :] = k[t]
-            v_pages[page, :, p % page_size, :] = v[t]
+            v_pages[page, :, p % page_size, :] = raw_v[t]
+
+    @staticmethod
+    def _turn_pairs(x, pos, inv_freq, pairing, magnitude=1.0):
+        """x [T, ..., n] float: the leading 2 * len(inv_freq) elements of the last axis turn by position * inv_freq[i];
+        pair i is (2i, 2i + 1) ("interleaved") or (i, i + pairs) ("half"); cos and sin times ``magnitude``."""
+        if inv_freq is None:
+            return x
+        pairs = inv_freq.numel()
+        ang = pos.float()[:, None] * inv_freq.float()[None, :]
+        shape = [x.shape[0]] + [1] * (x.dim() - 2) + [pairs]
+        c, s = (ang.cos() * magnitude).reshape(shape), (ang.sin() * magnitude).reshape(shape)
+        out = x.clone()
+        if pairing == "interleaved":
+            u, v = x[..., 0:2 * pairs:2], x[..., 1:2 * pairs:2]
+            out[..., 0:2 * pairs:2] = u * c - v * s
+            out[..., 1:2 * pairs:2] = v * c + u * s
+        else:
+            u, v = x[..., :pairs], x[..., pairs:2 * pairs]
+            out[..., :pairs] = u * c - v * s
+            out[..., pairs:2 * pairs] = v * c + u * s
+        return out
 
     def silu_mul(self, gate_up, out):
         I = out.shape[-1]
@@ -321,13 +357,15 @@ class TorchOps:
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
                         token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None,
-                        value_dim=None, keep_first=0, sink=None, gate=None):
+                        value_dim=None, keep_first=0, sink=None, gate=None, chunk=None, softcap=None):
         T = out.shape[0]
         D = head_dim
         group = num_heads // num_kv_heads
         for t in range(T):
             p = int(positions[t])
             lo = max(0, p - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, p // chunk * chunk)
             table = block_table[int(token_seq[t])]
             js = torch.cat([torch.arange(0, min(keep_first, lo)), torch.arange(lo, p + 1)])
             pages = table[(js // page_size).to(table.device)].long()
@@ -338,6 +376,8 @@ class TorchOps:
             kh = keys.repeat_interleave(group, dim=1)  # [n, nq, D]
             vh = vals.repeat_interleave(group, dim=1)
             scores = torch.einsum("hd,nhd->hn", qt, kh) * scale
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)
             if sink is not None:  # one more score that has no value
                 scores = torch.cat([scores, torch.full((num_heads, 1), float(sink), device=scores.device)], dim=-1)
                 probs = torch.softmax(scores, dim=-1)[:, :-1]
@@ -347,6 +387,32 @@ class TorchOps:
             if gate is not None:
                 res = res * torch.sigmoid(gate[t].float())
             out[t] = res.to(out.dtype)
+        return out
+
+    def differential_attention(self, q, q_stride, *, num_heads, num_kv_heads, map_dim, value_dim, k_pages, v_pages,
+                               block_table, token_seq, positions, out, page_size, scale, lam, eps, out_scale,
+                               window=None, chunk=None, step=None):
+        T = out.shape[0]
+        D = map_dim
+        group = num_heads // num_kv_heads
+        for t in range(T):
+            p = int(positions[t])
+            lo = max(0, p - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, p // chunk * chunk)
+            table = block_table[int(token_seq[t])]
+            js = torch.arange(lo, p + 1)
+            pages = table[(js // page_size).to(table.device)].long()
+            offs = (js % page_size).to(pages.device)
+            keys = k_pages[pages, :, offs, :].float().repeat_interleave(group, dim=1)  # [n, nq, 2D]
+            vals = v_pages[pages, :, offs, :].float().repeat_interleave(group, dim=1)  # [n, nq, Dv]
+            qt = q[t, : num_heads * 2 * D].reshape(num_heads, 2, D).float()
+            kk = keys.reshape(-1, num_heads, 2, D)
+            probs = torch.softmax(torch.einsum("hmd,nhmd->hmn", qt, kk) * scale, dim=-1)
+            a = torch.einsum("hmn,nhd->hmd", probs, vals)
+            o = a[:, 0] - lam * a[:, 1]
+            o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+            out[t] = o.reshape(-1).to(out.dtype)
         return out
 
     # ---- attention through a latent ------------------------------------------------------
@@ -366,15 +432,18 @@ class TorchOps:
         return out
 
     def latent_norm_rope_store(self, down, *, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, inv_freq, positions,
-                               token_seq, block_table, pages, page_size, write, q_out):
+                               token_seq, block_table, pages, page_size, write, q_out, pairing="interleaved",
+                               magnitude=1.0):
         x = down.float()
-        a = x[:, :q_rank]
-        q_out.copy_(((a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps)) * q_weight.float()).to(q_out.dtype))
+        if q_rank:
+            a = x[:, :q_rank]
+            q_out.copy_(((a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps)) * q_weight.float()).to(q_out.dtype))
         if not write:
             return
         c = x[:, q_rank:q_rank + kv_rank]
         c = (c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps)) * kv_weight.float()
-        k = self._turn(x[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim], positions.long(), inv_freq)
+        k = self._turn_pairs(x[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim], positions.long(), inv_freq, pairing,
+                             magnitude)
         row = torch.cat([c, k], dim=-1).to(pages.dtype)
         for t in range(down.shape[0]):
             p = int(positions[t])
@@ -386,8 +455,8 @@ class TorchOps:
         out.copy_(torch.einsum("thk,hnk->thn", x.float(), weight.float()).to(out.dtype))
         return out
 
-    def rotate_heads(self, x, out, *, positions, inv_freq):
-        out.copy_(self._turn(x.float(), positions.long(), inv_freq).to(out.dtype))
+    def rotate_heads(self, x, out, *, positions, inv_freq, pairing="interleaved", magnitude=1.0):
+        out.copy_(self._turn_pairs(x.float(), positions.long(), inv_freq, pairing, magnitude).to(out.dtype))
         return out
 
     def latent_attention(self, q, *, pages, value_dim, block_table, token_seq, positions, sink, out, page_size, scale,
