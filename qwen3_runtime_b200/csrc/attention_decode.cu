@@ -46,12 +46,14 @@ struct NewToken {
 // What some designs add to the attention.  keep: with a window, the sequence's first `keep` tokens stay
 // visible.  sink_log2: a score (times log2 e) that has no value and joins the softmax's denominator; minus
 // infinity for none.  gate: null, or rows [tokens][gate_stride] whose first heads * D values gate the result
-// by their sigmoid.
+// by their sigmoid.  cap_raw: scores are capped, score <- cap * tanh(score / cap) after the scale; given in the
+// unscaled dot product's units (cap / scale), 0 for none.
 struct Extras {
   int keep = 0;
   float sink_log2 = -INFINITY;
   const bf16* gate = nullptr;
   int gate_stride = 0;
+  float cap_raw = 0.f;
 };
 
 // The keys a token at position kv_len - 1 sees are numbered consecutively: the window's keys keep their
@@ -412,6 +414,13 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
       mma_bf16(s[0], qa[ks], kb[0], kb[1]);
       mma_bf16(s[1], qa[ks], kb[2], kb[3]);
     }
+    if (ex.cap_raw > 0.f) {  // capped scores (exact tanhf, fp32)
+      const float inv_cap = 1.f / ex.cap_raw;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e] = ex.cap_raw * tanhf(s[n][e] * inv_cap);
+    }
     // mask, running max
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -659,9 +668,10 @@ Q3_EXPORT int q3_paged_attention_decode_sink(const void* q, int q_stride, const 
                                              float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps,
                                              float scale, int window, int num_splits, int* tickets,
                                              const int* longest_len, int keep_first, int has_sink, float sink,
-                                             const void* gate, int gate_stride, cudaStream_t stream) {
-  if (keep_first < 0 || (gate && gate_stride < nq * D)) return Q3_ERR_ARGUMENT;
+                                             const void* gate, int gate_stride, float softcap, cudaStream_t stream) {
+  if (keep_first < 0 || (gate && gate_stride < nq * D) || softcap < 0.f || !(scale > 0.f)) return Q3_ERR_ARGUMENT;
   Extras ex;
+  ex.cap_raw = softcap / scale;
   ex.keep = window > 0 ? keep_first : 0;
   ex.sink_log2 = has_sink ? sink * 1.4426950408889634f : -INFINITY;
   ex.gate = (const bf16*)gate;
@@ -678,7 +688,8 @@ Q3_EXPORT int q3_paged_attention_decode_sink(const void* q, int q_stride, const 
 // null.  The key and value of the newest token are written to their pages; q is not written
 // back.  `error_word` (may be null) is set to Q3_ERR_POSITION if a newest position lies beyond
 // the tables; that token is then left unrotated and the result is invalid.
-// (keep_first, has_sink, sink, gate, gate_stride: as in q3_paged_attention_decode_sink.)
+// (keep_first, has_sink, sink, gate, gate_stride, softcap: as in q3_paged_attention_decode_sink; softcap: scores
+// become softcap * tanh(score / softcap) after the scale, 0 for none.)
 Q3_EXPORT int q3_paged_attention_decode_fused_sink(const void* qkv, int q_stride, void* kpages, void* vpages,
                                                    const int* block_table, int max_pages, const int* kv_lens,
                                                    const int* cu_seqlens, const int* seq_list, void* out,
@@ -687,15 +698,16 @@ Q3_EXPORT int q3_paged_attention_decode_fused_sink(const void* qkv, int q_stride
                                                    const float* k_w, float eps, const float* cos_t,
                                                    const float* sin_t, int max_pos, int pairing, int* error_word,
                                                    int* tickets, const int* longest_len, int keep_first, int has_sink,
-                                                   float sink, const void* gate, int gate_stride,
+                                                   float sink, const void* gate, int gate_stride, float softcap,
                                                    cudaStream_t stream) {
   if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
-  if (keep_first < 0 || (gate && gate_stride < nq * D)) return Q3_ERR_ARGUMENT;
+  if (keep_first < 0 || (gate && gate_stride < nq * D) || softcap < 0.f || !(scale > 0.f)) return Q3_ERR_ARGUMENT;
   const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
                          (uintptr_t)cos_t | (uintptr_t)sin_t;
   if (bits & 15) return Q3_ERR_UNSUPPORTED;
   NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing};
   Extras ex;
+  ex.cap_raw = softcap / scale;
   ex.keep = window > 0 ? keep_first : 0;
   ex.sink_log2 = has_sink ? sink * 1.4426950408889634f : -INFINITY;
   ex.gate = (const bf16*)gate;
@@ -716,7 +728,7 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
   return q3_paged_attention_decode_fused_sink(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens,
                                               cu_seqlens, seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale,
                                               window, num_splits, q_w, k_w, eps, cos_t, sin_t, max_pos, pairing,
-                                              error_word, tickets, longest_len, 0, 0, 0.f, nullptr, 0, stream);
+                                              error_word, tickets, longest_len, 0, 0, 0.f, nullptr, 0, 0.f, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

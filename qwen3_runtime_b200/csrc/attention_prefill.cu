@@ -34,7 +34,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                          bf16* __restrict__ out, int num_seqs, int nq, int nkv, int ps, float scale_log2,
                          int window, int skip_single, int keep, float sink_log2, const bf16* __restrict__ gate,
-                         int gate_stride) {
+                         int gate_stride, float cap_raw) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -185,6 +185,13 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         mma_bf16(s[2 * nn + 1], qa[ks], kb[2], kb[3]);
       }
     }
+    if (cap_raw > 0.f) {  // capped scores: cap * tanh(score / cap) in the unscaled product's units (exact tanhf)
+      const float inv_cap = 1.f / cap_raw;
+#pragma unroll
+      for (int n = 0; n < TILE / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e] = cap_raw * tanhf(s[n][e] * inv_cap);
+    }
     // mask where the tile crosses the diagonal or the window's edge
     if (key0 + TILE - 1 > wp_min || key0 < wlo_max) {
 #pragma unroll
@@ -274,7 +281,7 @@ template <int D>
 int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                    int max_pages, const int* kv_lens, const int* cu_seqlens, bf16* out, int num_seqs, int num_work,
                    int nq, int nkv, int ps, float scale, int window, int skip_single, int keep, float sink_log2,
-                   const bf16* gate, int gate_stride, cudaStream_t stream) {
+                   const bf16* gate, int gate_stride, float softcap, cudaStream_t stream) {
   const size_t smem = (size_t)BLOCK_M * D * 2 + (size_t)STAGES * 2 * TILE * D * 2;
   static bool configured_on[Q3_MAX_DEVICES];
   bool& configured = configured_on[q3_current_device()];
@@ -288,7 +295,7 @@ int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* 
   prefill_attention_kernel<D><<<grid, THREADS, smem, stream>>>(q, q_stride, kpages, vpages, block_table, max_pages,
                                                                kv_lens, cu_seqlens, out, num_seqs, nq, nkv, ps,
                                                                scale * 1.4426950408889634f, window, skip_single,
-                                                               keep, sink_log2, gate, gate_stride);
+                                                               keep, sink_log2, gate, gate_stride, softcap / scale);
   return q3_launch_status();
 }
 
@@ -299,16 +306,17 @@ int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* 
 // (their rows of `out` are not written).
 // keep_first: with a window, the sequence's first tokens stay visible.  has_sink / sink: a score without a
 // value in the softmax's denominator.  gate: null, or rows of gate_stride values of which the first nq * D
-// gate the heads' outputs by their sigmoid.
+// gate the heads' outputs by their sigmoid.  softcap: scores become softcap * tanh(score / softcap) after the
+// scale; 0 for none.
 Q3_EXPORT int q3_paged_attention_prefill_sink(const void* q, int q_stride, const void* kpages, const void* vpages,
                                               const int* block_table, int max_pages, const int* kv_lens,
                                               const int* cu_seqlens, void* out, int num_seqs, int num_work, int nq,
                                               int nkv, int D, int ps, float scale, int window, int skip_single,
                                               int keep_first, int has_sink, float sink, const void* gate,
-                                              int gate_stride, cudaStream_t stream) {
+                                              int gate_stride, float softcap, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_seqs < 0 || num_work < 0) return Q3_ERR_ARGUMENT;
-  if (keep_first < 0 || (gate && gate_stride < nq * D)) return Q3_ERR_ARGUMENT;
+  if (keep_first < 0 || (gate && gate_stride < nq * D) || softcap < 0.f || !(scale > 0.f)) return Q3_ERR_ARGUMENT;
   if (q_stride % 8 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
   if (num_work == 0) return Q3_OK;
   const int keep = window > 0 ? keep_first : 0;
@@ -316,11 +324,11 @@ Q3_EXPORT int q3_paged_attention_prefill_sink(const void* q, int q_stride, const
   if (D == 64)
     return launch_prefill<64>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                               max_pages, kv_lens, cu_seqlens, (bf16*)out, num_seqs, num_work, nq, nkv, ps, scale,
-                              window, skip_single, keep, sink_log2, (const bf16*)gate, gate_stride, stream);
+                              window, skip_single, keep, sink_log2, (const bf16*)gate, gate_stride, softcap, stream);
   if (D == 128)
     return launch_prefill<128>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                                max_pages, kv_lens, cu_seqlens, (bf16*)out, num_seqs, num_work, nq, nkv, ps, scale,
-                               window, skip_single, keep, sink_log2, (const bf16*)gate, gate_stride, stream);
+                               window, skip_single, keep, sink_log2, (const bf16*)gate, gate_stride, softcap, stream);
   return Q3_ERR_UNSUPPORTED;
 }
 
@@ -331,5 +339,5 @@ Q3_EXPORT int q3_paged_attention_prefill(const void* q, int q_stride, const void
                                          cudaStream_t stream) {
   return q3_paged_attention_prefill_sink(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, out,
                                          num_seqs, num_work, nq, nkv, D, ps, scale, window, skip_single, 0, 0, 0.f,
-                                         nullptr, 0, stream);
+                                         nullptr, 0, 0.f, stream);
 }

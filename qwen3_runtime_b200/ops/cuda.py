@@ -151,7 +151,7 @@ _SIGNATURES = {
         "q3_paged_attention_decode_sink": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
-                                           c_int, c_void_p],
+                                           c_int, c_float, c_void_p],
         "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
@@ -160,7 +160,7 @@ _SIGNATURES = {
                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
                                                  c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                 c_int, c_float, c_void_p, c_int, c_void_p],
+                                                 c_int, c_float, c_void_p, c_int, c_float, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -168,7 +168,7 @@ _SIGNATURES = {
                                        c_void_p],
         "q3_paged_attention_prefill_sink": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                            c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+                                            c_int, c_int, c_float, c_void_p, c_int, c_float, c_void_p],
     },
     "attention_prefill_tc": {
         "q3_paged_attention_prefill_tc": [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_long, c_void_p, c_int,
@@ -996,10 +996,13 @@ class CudaOps:
         keep_first = int(keep_first or 0) if window else 0
         plain = not keep_first and sink is None and gate is None  # what the tcgen05 kernel takes
         dense = out.stride(0) == num_heads * Dv and Dv == head_dim
-        chunk, softcap = int(chunk or 0), float(softcap or 0.0)
-        if chunk or softcap:
-            dense = False  # the specialised kernels know neither: the general kernel
         extras = dict(keep_first=keep_first, sink=sink, gate=gate)
+        chunk, softcap = int(chunk or 0), float(softcap or 0.0)
+        if chunk:
+            dense = False  # the specialised kernels know no chunks: the general kernel
+        if softcap:
+            plain = False  # the tcgen05 kernel knows no capped scores; the other specialised kernels do
+            extras["softcap"] = softcap
         if gate is not None and (gate.stride(1) != 1 or gate.shape != (T, num_heads * Dv) or gate.dtype != out.dtype):
             raise KernelError("paged_attention: the gate is [tokens, heads * value_dim] of the output's type")
         if Dv > 256 or out.stride(1) != 1:
@@ -1049,7 +1052,7 @@ class CudaOps:
                            block_table.shape[1], _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out),
                            step.num_seqs, work, num_heads, num_kv_heads, head_dim, page_size, float(scale),
                            int(window or 0), 1, keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
-                           gate.stride(0) if gate is not None else 0)
+                           gate.stride(0) if gate is not None else 0, softcap)
             if step.num_single:
                 singles = [kv for kv, n in zip(step.host_kv_lens, qlens) if n == 1]
                 longest = max(singles)
@@ -1187,7 +1190,7 @@ class CudaOps:
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
                                max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None,
-                               merge_kernel=False, longest=None, keep_first=0, sink=None, gate=None):
+                               merge_kernel=False, longest=None, keep_first=0, sink=None, gate=None, softcap=None):
         """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
         ``new_token`` (q_weight, k_weight, eps, cos, sin, optionally pairing): ``q`` is the raw q/k/v
         projection and the kernel also does the work of :meth:`qk_norm_rope_store` for the newest
@@ -1197,7 +1200,7 @@ class CudaOps:
         ``num_splits`` is the slice count of the longest sequence (a shorter one gets fewer slices of
         about the same length); ``longest``: a device int32 holding the longest of the sequences'
         lengths, when the caller has it (else every block works it out from ``kv_lens``).
-        ``keep_first``, ``sink``, ``gate``: as in :meth:`paged_attention`."""
+        ``keep_first``, ``sink``, ``gate``, ``softcap``: as in :meth:`paged_attention`."""
         if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
             raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
         keep_first = int(keep_first or 0) if window else 0
@@ -1228,14 +1231,14 @@ class CudaOps:
                        _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
                        self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets), _ptr(longest),
                        keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
-                       gate.stride(0) if gate is not None else 0)
+                       gate.stride(0) if gate is not None else 0, float(softcap or 0.0))
             return out
         self._call("attention_decode", "q3_paged_attention_decode_sink", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                    num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits,
                    _ptr(tickets), _ptr(longest), keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
-                   gate.stride(0) if gate is not None else 0)
+                   gate.stride(0) if gate is not None else 0, float(softcap or 0.0))
         return out
 
     # ---- matrix products ----------------------------------------------------------------

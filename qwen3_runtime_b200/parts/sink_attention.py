@@ -101,9 +101,9 @@ class SinkWindowAttention(Part):
     def _specialised(self) -> bool:
         """Keys and values of one size that the split-KV decode kernel (64, 128, 256) and the tensor-core prompt
         kernel (64, 128) take (ops.paged_attention sends a dense output there), with the window's kept first tokens, the
-        sink and the gate."""
+        sink, the gate and capped scores."""
         return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128, 256)
-                and self.num_heads // self.num_kv_heads <= 16 and not self.softcap and not self.chunk)
+                and self.num_heads // self.num_kv_heads <= 16 and not self.chunk)
 
     def _slices_key(self):
         reach = self.window + self.keep_first if self.window else None  # the most keys a token sees
@@ -135,7 +135,7 @@ class SinkWindowAttention(Part):
         fusable = getattr(ops, "decode_new_token_ok", None)
         rotary = self.position.style == "rotary"
         if (fusable is not None and step.decode_only and cache.writes and self._specialised() and not rotary
-                and not self.values_are_keys
+                and not self.values_are_keys and not self.softcap
                 and s[1] == H * D and s[2] == (H + G) * D  # q, k and v heads side by side, as that kernel reads them
                 and fusable(proj, num_heads=H, num_kv_heads=G, head_dim=D, cos=None, q_weight=self.q_norm,
                             k_weight=self.k_norm)):

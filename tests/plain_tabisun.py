@@ -11,6 +11,12 @@ import math
 
 import torch
 
+ACTIVATIONS = None  # a dtype: products' results and sublayer inputs are rounded to it (a model of 16-bit activations)
+
+
+def _r(x):
+    return x if ACTIVATIONS is None else x.to(ACTIVATIONS).to(x.dtype)
+
 
 def layer_norm(x, w, eps):
     mu = x.mean(-1, keepdim=True)
@@ -103,51 +109,63 @@ def chunked(T, size):
     return (i[None, :] <= i[:, None]) & ((i[None, :] // size) == (i[:, None] // size))
 
 
+def differential_core(q, k, v, scale, lam, chunk, eps, out_scale):
+    """q ``[T, H, 2, D]``, k ``[T, G, 2, D]`` (normed), v ``[T, G, Dv]`` -> ``[T, H, Dv]``: per head
+    a1 - lam * a2 over the same values, divided by its root mean square, times ``out_scale``."""
+    T, H = q.shape[0], q.shape[1]
+    rep = H // k.shape[1]
+    visible = chunked(T, chunk) if chunk else causal(T)
+    outs = []
+    for hq in range(H):
+        g = hq // rep
+        a = [softmax_rows(((q[:, hq, which] @ k[:, g, which].T) * scale)[None], visible)[0] @ v[:, g]
+             for which in range(2)]
+        outs.append(rms_norm(a[0] - lam * a[1], None, eps) * out_scale)
+    return torch.stack(outs, 1)
+
+
 def differential_attention(h, t, p, m, eps):
     """Two score maps per head over shared values; o = a1 - lambda a2, unit RMS per head, times (1 - diff)."""
     T = h.shape[0]
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ t[p + "q"].T).view(T, H, 2, D)
-    k = (h @ t[p + "k"].T).view(T, G, 2, D)
-    v = (h @ t[p + "v"].T).view(T, G, Dv)
-    q = rms_norm(q, t[p + "q.norm"], eps)
-    k = rms_norm(k, t[p + "k.norm"], eps)
+    q = _r(rms_norm(_r(h @ t[p + "q"].T).view(T, H, 2, D), t[p + "q.norm"], eps))
+    k = _r(rms_norm(_r(h @ t[p + "k"].T).view(T, G, 2, D), t[p + "k.norm"], eps))
+    v = _r(h @ t[p + "v"].T).view(T, G, Dv)
     lam = (torch.exp((t[p + "lq1"] * t[p + "lk1"]).sum()) - torch.exp((t[p + "lq2"] * t[p + "lk2"]).sum())
            + m["diff"])
-    visible = chunked(T, m["mask"]["size"])
-    rep = H // G
+    chunk = (m.get("mask") or {}).get("size")
+    o = _r(differential_core(q, k, v, m["scale"], lam, chunk, eps, 1 - m["diff"]))
+    return o.reshape(T, H * Dv) @ t[p + "o"].T
+
+
+def capped_core(q, k, v, scale, softcap):
+    """q ``[T, H, D]``, k ``[T, G, D]``, v ``[T, G, Dv]`` -> ``[T, H, Dv]``: causal softmax of capped scores."""
+    T, H = q.shape[0], q.shape[1]
+    rep = H // k.shape[1]
     outs = []
     for hq in range(H):
         g = hq // rep
-        a = []
-        for which in range(2):
-            s = (q[:, hq, which] @ k[:, g, which].T) * m["scale"]
-            a.append(softmax_rows(s[None], visible)[0] @ v[:, g])
-        o = a[0] - lam * a[1]
-        outs.append(rms_norm(o, None, eps) * (1 - m["diff"]))
-    return torch.cat(outs, -1) @ t[p + "o"].T
+        s = (q[:, hq] @ k[:, g].T) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        outs.append(softmax_rows(s[None], causal(T))[0] @ v[:, g])
+    return torch.stack(outs, 1)
 
 
 def key_value_attention(h, t, p, m, eps):
     """Grouped heads whose values are the projected keys (before norm and rotation); capped scores."""
     T = h.shape[0]
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
-    q = (h @ t[p + "q"].T).view(T, H, D)
-    k_raw = (h @ t[p + "k"].T).view(T, G, D)
-    pos = torch.arange(T)
-    rot = m["rot"]
-    freqs = scaled_frequencies_by_wavelength(rot["dims"], rot["base"], rot.get("scaling"), h.dtype)
-    q = rotate(rms_norm(q, t[p + "q.norm"], eps), pos, freqs, "interleaved")
-    k = rotate(rms_norm(k_raw, t[p + "k.norm"], eps), pos, freqs, "interleaved")
-    visible = causal(T)
-    rep = H // G
-    outs = []
-    for hq in range(H):
-        g = hq // rep
-        s = (q[:, hq] @ k[:, g].T) * m["scale"]
-        s = m["softcap"] * torch.tanh(s / m["softcap"])
-        outs.append(softmax_rows(s[None], visible)[0] @ k_raw[:, g])
-    return torch.cat(outs, -1) @ t[p + "o"].T
+    q = _r(h @ t[p + "q"].T).view(T, H, D)
+    k_raw = _r(h @ t[p + "k"].T).view(T, G, D)
+    q, k = rms_norm(q, t[p + "q.norm"], eps), rms_norm(k_raw, t[p + "k.norm"], eps)
+    rot = m.get("rot")
+    if rot:
+        pos = torch.arange(T)
+        freqs = scaled_frequencies_by_wavelength(rot["dims"], rot["base"], rot.get("scaling"), h.dtype)
+        q, k = rotate(q, pos, freqs, "interleaved"), rotate(k, pos, freqs, "interleaved")
+    o = _r(capped_core(_r(q), _r(k), k_raw, m["scale"], m.get("softcap")))
+    return o.reshape(T, H * D) @ t[p + "o"].T
 
 
 def latent_attention(h, t, p, m, eps):
@@ -155,9 +173,9 @@ def latent_attention(h, t, p, m, eps):
     the softmax; a sigmoid gate on the heads' outputs."""
     T = h.shape[0]
     H, D, R, Dv, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    q = (h @ t[p + "q"].T).view(T, H, D + R)
-    down = h @ t[p + "dkv"].T
-    c = rms_norm(down[:, :C], t[p + "dkv.norm"], eps)
+    q = _r(h @ t[p + "q"].T).view(T, H, D + R)
+    down = _r(h @ t[p + "dkv"].T)
+    c = _r(rms_norm(down[:, :C], t[p + "dkv.norm"], eps))
     rot = m["rot"]
     freqs, magnitude = ramped_frequencies(rot["dims"], rot["base"], rot.get("scaling"), h.dtype)
     pos = torch.arange(T)
@@ -167,8 +185,8 @@ def latent_attention(h, t, p, m, eps):
     v = (c @ t[p + "uv"].T).view(T, H, Dv)
     scores = torch.einsum("ihd,jhd->hij", q[..., :D], k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)
     w = softmax_rows(scores * m["scale"], causal(T), sink=t[p + "sink"].to(h.dtype))
-    o = torch.einsum("hij,jhd->ihd", w, v).reshape(T, H * Dv)
-    o = o * torch.sigmoid(h @ t[p + "g"].T)
+    o = _r(torch.einsum("hij,jhd->ihd", w, v).reshape(T, H * Dv))
+    o = _r(o * torch.sigmoid(_r(h @ t[p + "g"].T)))
     return o @ t[p + "o"].T
 
 
@@ -178,11 +196,22 @@ MIXERS = {"attention": differential_attention, "attention_2": key_value_attentio
 
 def dense_feed_forward(h, t, p):
     z = h @ t[p + "gate"].T
-    return ((z * torch.sigmoid(z)) * (h @ t[p + "up"].T)) @ t[p + "down"].T
+    return _r((z * torch.sigmoid(z)) * (h @ t[p + "up"].T)) @ t[p + "down"].T
 
 
-def forward(config, tensors, tokens, dtype=torch.float64, with_streams=False):
-    """Logits ``[T, vocab]`` of one sequence (and the stream after every layer run)."""
+def forward(config, tensors, tokens, dtype=torch.float64, with_streams=False, activations=None):
+    """Logits ``[T, vocab]`` of one sequence (and the stream after every layer run).  ``activations``: a
+    narrower type that sublayer inputs, products' results and sublayer outputs are rounded to, the stream,
+    norms, scores and softmax staying in ``dtype``."""
+    global ACTIVATIONS
+    ACTIVATIONS = activations
+    try:
+        return _forward(config, tensors, tokens, dtype, with_streams)
+    finally:
+        ACTIVATIONS = None
+
+
+def _forward(config, tensors, tokens, dtype, with_streams):
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps = config["norm"]["eps"]
     x = t["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -192,11 +221,11 @@ def forward(config, tensors, tokens, dtype=torch.float64, with_streams=False):
         if src is None:
             src = i
         p = f"l{src}."
-        x = x + layer_norm(MIXERS[layer["type"]](x, t, p + "mix.", layer["mixer"], eps), t[p + "norm1"], eps)
+        x = x + layer_norm(_r(MIXERS[layer["type"]](_r(x), t, p + "mix.", layer["mixer"], eps)), t[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + layer_norm(dense_feed_forward(x, t, p + "mlp."), t[p + "norm2"], eps)
+            x = x + layer_norm(_r(dense_feed_forward(_r(x), t, p + "mlp.")), t[p + "norm2"], eps)
         streams.append(x)
-    logits = layer_norm(x, t["final.norm"], eps) @ t["head"].T
+    logits = _r(layer_norm(x, t["final.norm"], eps)) @ t["head"].T
     cap = config.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
