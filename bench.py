@@ -50,6 +50,11 @@ kinds and a roofline fraction per kind):
                    shift, a bonus and per-channel decays; attention with a sink, a window that keeps the first
                    tokens and an output gate; grouped routing with identity experts; two grouped norms per
                    layer) at two layer sizes beside the Puladra design at equal sizes, its closest relative;
+* ``tabisun``      the Tabisun design (differential attention under a chunked mask, attention whose values are
+                   the keys with scaled rotary positions and capped scores, attention through a latent with a
+                   sink and an output gate, layer norms on the sublayers' outputs only, a layer that runs another
+                   layer's weights) at two layer sizes beside the Logesun design at equal sizes, its closest
+                   relative (dense feed-forwards in both);
 * ``decode``, ``latency``, ``batch8``, ``throughput``, ``prefill``, ``longctx``: the six closed
                    batches of the reference's own harness (bench/workloads.py:34-43) at Qwen3-4B
                    sizes, with its token budget rule (bench/workloads.py:52-64).
@@ -100,7 +105,7 @@ BASELINE_TOK_S = 693.26
 # (concurrency = requests, prompt tokens, output tokens) of the reference's closed batches
 CLOSED_CASES = {"decode": (1, 256, 512), "latency": (1, 512, 128), "batch8": (8, 256, 128),
                 "throughput": (16, 256, 128), "prefill": (1, 2048, 16), "longctx": (1, 8192, 64)}
-WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", "puladra", "medilix", *CLOSED_CASES)
+WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", "puladra", "medilix", "tabisun", *CLOSED_CASES)
 
 # Layer sizes for the Puladra design that resemble real models of its kinds of layer: gated linear
 # attention with keys of half and values of the full width, windowed attention with grouped key/value
@@ -131,6 +136,21 @@ MEDILIX_SIZES = {
     "w4096": dict(width=4096, heads=32, mem=dict(heads=32, dim=64, vdim=128), wkv=dict(heads=64, dim=64, rank=64),
                   att=dict(heads=32, kv_heads=8, dim=128, vdim=128, window=2048, keep=64),
                   experts=28, identity=4, top=4, expert_ff=2048, groups=(8, 4), norm_groups=4, layers=4, vocab=32000),
+}
+
+# Layer sizes for the Tabisun design: differential attention with two maps of 64 per head over values of 128
+# (grouped key/value heads, chunks of 2,048 tokens), attention with grouped heads of 128 whose values are the
+# keys (half of each head rotated), attention through a latent of 512 with a rotated key part of 64, dense
+# SwiGLU feed-forwards.  Four layers: one of each mixer and a fourth that runs the first one's weights.
+# Beside each runs Logesun (attention through a latent, norms around every sublayer, dense feed-forwards)
+# with the same width, heads, latent sizes and feed-forward width.
+TABISUN_SIZES = {
+    "w2048": dict(width=2048, ff=8192, vocab=32000, layers=4, chunk=2048,
+                  diff=dict(heads=16, kv_heads=4, dim=64, vdim=128), kv=dict(heads=16, kv_heads=4, dim=128, rot=64),
+                  latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512)),
+    "w4096": dict(width=4096, ff=12288, vocab=32000, layers=4, chunk=2048,
+                  diff=dict(heads=32, kv_heads=8, dim=64, vdim=128), kv=dict(heads=32, kv_heads=8, dim=128, rot=64),
+                  latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512)),
 }
 
 # Layer sizes for the Logesun design (attention through a latent with a window and a sink, routed
@@ -674,6 +694,48 @@ def _medilix_config(z: dict):
                          embed_scale=1.0, bigram=BigramConfig(buckets=65521, mul_prev=40503, mul_cur=1), layers=layers)
 
 
+def _tabisun_config(z: dict):
+    from qwen3_runtime_b200.config import TabisunConfig
+    from qwen3_runtime_b200.config.tabisun_config import (DifferentialConfig, KeyValueConfig, LatentConfig,
+                                                          RotaryConfig, TabisunLayerConfig)
+
+    d, k, l = z["diff"], z["kv"], z["latent"]
+    diff = DifferentialConfig(heads=d["heads"], kv_heads=d["kv_heads"], dim=d["dim"], vdim=d["vdim"],
+                              scale=d["dim"] ** -0.5, diff=0.6, chunk=z["chunk"])
+    kv = KeyValueConfig(heads=k["heads"], kv_heads=k["kv_heads"], dim=k["dim"], vdim=k["dim"], scale=k["dim"] ** -0.5,
+                        softcap=50.0, rot=RotaryConfig(dims=k["rot"], base=5e5, scaling=(
+                            ("factor", 8.0), ("low", 1.0), ("high", 4.0), ("original", 8192.0))))
+    latent = LatentConfig(heads=l["heads"], dim=l["dim"], rot_dim=l["rot_dim"], vdim=l["vdim"], kv_rank=l["kv_rank"],
+                          scale=(l["dim"] + l["rot_dim"]) ** -0.5,
+                          rot=RotaryConfig(dims=l["rot_dim"], base=1e4, scaling=(
+                              ("factor", 40.0), ("original", 4096.0), ("fast", 32.0), ("slow", 1.0))))
+    layers = (TabisunLayerConfig("attention", diff, z["ff"]), TabisunLayerConfig("attention_2", kv, z["ff"]),
+              TabisunLayerConfig("latent_attention", latent, z["ff"]),
+              TabisunLayerConfig("attention", diff, z["ff"], weights_of=0))
+    return TabisunConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, layers=layers, logit_softcap=30.0)
+
+
+def _logesun_twin_config(z: dict):
+    """Logesun at the sizes of a Tabisun entry: every layer attends through a latent of the same sizes (its
+    queries through a latent of their own) without a window, and has the same dense feed-forward."""
+    from qwen3_runtime_b200.config import LogesunConfig
+    from qwen3_runtime_b200.config.logesun_config import FeedForwardConfig, LatentAttentionConfig, LogesunLayerConfig
+
+    l = z["latent"]
+    mixer = LatentAttentionConfig(heads=l["heads"], dim=l["dim"], rot_dim=l["rot_dim"], vdim=l["vdim"],
+                                  q_rank=3 * z["width"] // 8, kv_rank=l["kv_rank"],
+                                  scale=(l["dim"] + l["rot_dim"]) ** -0.5, rot_dims=l["rot_dim"], rot_base=10000.0,
+                                  window=None)
+    dense = FeedForwardConfig(kind="dense", ff=z["ff"])
+    layers = tuple(LogesunLayerConfig("latent_attention", mixer, dense) for _ in range(z["layers"]))
+    return LogesunConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, layers=layers)
+
+
+def run_tabisun(args, pk) -> dict:
+    return run_design_beside_dense(args, pk, "tabisun", "Tabisun", TABISUN_SIZES, _tabisun_config,
+                                   twin=("logesun", _logesun_twin_config, "the Logesun design"))
+
+
 def _puladra_twin_config(z: dict):
     """Puladra at the sizes of a Medilix entry: its gated linear attention has the mlstm's heads and sizes, its
     windowed attention the attention's, its retention the wkv's."""
@@ -771,6 +833,8 @@ def run_workload_ours(args) -> dict:
         return run_puladra(args, pk)
     if args.workload == "medilix":
         return run_medilix(args, pk)
+    if args.workload == "tabisun":
+        return run_tabisun(args, pk)
     cases = workload_prompts(args.workload, np)
     results, cfg, build_s, engine = {}, None, 0.0, None
     clocks = ClockSampler()
@@ -1028,7 +1092,7 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.workload == "default":
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
-    elif args.workload in ("logesun", "puladra", "medilix") and args.impl == "reference":
+    elif args.workload in ("logesun", "puladra", "medilix", "tabisun") and args.impl == "reference":
         result = {"impl": "reference", "workload": args.workload,
                   "unavailable": "the reference has no model of this design (it serves Qwen3 dense only)"}
     else:

@@ -128,6 +128,14 @@ _SIGNATURES = {
                                     c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                     c_float, c_float, c_float, c_void_p],
     },
+    "attention_diff": {
+        "q3_diff_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                      c_int, c_int, c_float, c_float, c_float, c_void_p],
+        "q3_diff_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                     c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    },
     "linear_state": {
         "q3_decayed_state_scan": [c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long,
                                   c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p,
@@ -245,6 +253,7 @@ class CudaOps:
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
         self.latent_attention_tc = True     # False: attention over latent rows always on the general kernel
         self.experts_tc = True              # False: the experts' products always on the FMA kernels
+        self.differential_tc = True         # False: differential attention always on the general kernel
         self._tickets: torch.Tensor | None = None
         self._argmax_tickets: torch.Tensor | None = None
         # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
@@ -1087,7 +1096,42 @@ class CudaOps:
         if k_pages.shape[-1] != 2 * map_dim or v_pages.shape[-1] != value_dim:
             raise KernelError("differential_attention: key pages hold both maps, value pages the values")
         if self.timing is not None and step is not None:
-            self._costs(*self._attention_cost(step, num_heads, num_kv_heads, map_dim + value_dim // 2, out))
+            # a key row of two maps and a value row per key; two score products and two weighted sums per pair
+            nbytes, _ = self._attention_cost(step, num_heads, num_kv_heads, map_dim + value_dim // 2, out)
+            _, flops = self._attention_cost(step, num_heads, num_kv_heads, map_dim + value_dim, out)
+            self._costs(nbytes, flops)
+        group = num_heads // num_kv_heads
+        if (self.differential_tc and step is not None and out.dtype == torch.bfloat16 and q_stride % 8 == 0
+                and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+            if (step.decode_only and group in (1, 2, 4, 8) and map_dim % 8 == 0 and value_dim % 32 == 0
+                    and value_dim <= 128):
+                # one token per sequence: the keys cut into slices so that about two blocks per SM work.  The
+                # count comes from an upper bound of the lengths (in a captured step: the block-table width it
+                # was captured for), never from the lengths of the moment.
+                bound = step.captured_width * page_size or step.max_kv_len
+                for limit in (window, chunk):
+                    if limit:
+                        bound = min(bound, int(limit))
+                blocks = max(1, step.num_seqs * num_kv_heads)
+                splits = max(1, min(-(-bound // 256), (2 * self.SM_COUNT) // blocks, 64))
+                mid = torch.empty(step.num_seqs * num_heads * splits * 2 * (value_dim + 2), dtype=torch.float32,
+                                  device=out.device)
+                self.launches += 1  # the merge of the slices
+                self._call("attention_diff", "q3_diff_attention_decode", "differential_attention_decode", _ptr(q),
+                           q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                           _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out), out.stride(0), _ptr(mid),
+                           step.num_seqs, num_heads, num_kv_heads, map_dim, value_dim, page_size, float(scale),
+                           int(window or 0), int(chunk or 0), splits, float(lam), float(eps), float(out_scale))
+                return out
+            if (map_dim, value_dim) in ((32, 64), (64, 64), (64, 128), (128, 128)):
+                cu = step.host_cu_seqlens
+                work = sum(-(-(cu[b + 1] - cu[b]) * group // 128) for b in range(step.num_seqs) if cu[b + 1] > cu[b])
+                self._call("attention_diff", "q3_diff_attention_prefill", "differential_attention_tc", _ptr(q),
+                           q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                           _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out), out.stride(0), step.num_seqs, work,
+                           num_heads, num_kv_heads, map_dim, value_dim, page_size, float(scale), int(window or 0),
+                           int(chunk or 0), float(lam), float(eps), float(out_scale))
+                return out
         self._call("attention_generic", "q3_paged_attention_diff", "differential_attention", _dtype_code(out.dtype),
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads, num_kv_heads, map_dim,

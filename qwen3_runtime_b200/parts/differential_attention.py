@@ -11,7 +11,9 @@ Positions do not enter the scores.  What a token sees: every j <= i, or with ``w
 of them, or with ``chunk`` those of its own chunk (chunks of that many tokens counted from the sequence's
 first token).  The cache is one paged layer: a key row holds both maps of a key head side by side, so that
 one kernel scores both maps from one row and reads every value once for both sums; the subtraction and the
-heads' norm are that kernel's epilogue.
+heads' norm are that kernel's epilogue.  In bfloat16 prompt portions run on the tensor cores and steps of one
+token per sequence on a kernel that cuts the keys into slices (csrc/attention_diff.cu); float32, and sizes
+those kernels refuse, run the general kernel (csrc/attention_generic.cu).
 """
 
 from __future__ import annotations
@@ -68,7 +70,7 @@ class DifferentialAttention(Part):
 
     def kernel_groups(self):
         groups = ["rope_kv", "attention_generic"]
-        groups += ["gemm_f32"] if self.ctx.dtype == torch.float32 else ["gemm_small_m", "gemm_stream"]
+        groups += ["gemm_f32"] if self.ctx.dtype == torch.float32 else ["gemm_small_m", "gemm_stream", "attention_diff"]
         return groups
 
     def cache_spec(self):

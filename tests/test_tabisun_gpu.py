@@ -49,7 +49,12 @@ def test_attention_edges(ops, dtype):
     tc.case_differential_edges(dtype, ops, DEV)
     tc.case_differential_edges(dtype, ops, DEV, chunk=8, page_size=8, heads=1, kv_heads=1, D=20, Dv=8)
     tc.case_differential_edges(dtype, ops, DEV, chunk=33, page_size=16, heads=6, kv_heads=2, D=48, Dv=96, T=130)
+    # sizes that in bfloat16 run the tensor-core prompt kernel and the sliced decode kernel (groups of 4, 8, 2, 1;
+    # several slices; chunks that are no multiple of the key tile; no chunk at all)
     tc.case_differential_edges(dtype, ops, DEV, chunk=64, page_size=16, heads=4, kv_heads=1, D=64, Dv=128, T=200)
+    tc.case_differential_edges(dtype, ops, DEV, chunk=200, page_size=16, heads=8, kv_heads=1, D=32, Dv=64, T=700)
+    tc.case_differential_edges(dtype, ops, DEV, chunk=100, page_size=8, heads=4, kv_heads=2, D=64, Dv=64, T=330)
+    tc.case_differential_edges(dtype, ops, DEV, chunk=129, page_size=32, heads=2, kv_heads=2, D=128, Dv=128, T=420)
     tc.case_capped_far_key(dtype, ops, DEV)
     tc.case_capped_far_key(dtype, ops, DEV, chunk=100)
     tc.case_capped_far_key(dtype, ops, DEV, heads=8, kv_heads=2, D=64, T=400)
