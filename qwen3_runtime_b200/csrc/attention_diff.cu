@@ -13,9 +13,10 @@
 //                  for both maps; the subtraction and the head's norm are the epilogue.
 //   diff_decode    steps in which every sequence brings one token: a block per (sequence, kv head, slice of
 //                  the keys), 8 warps taking tiles of 32 keys in turn, a lane scoring one key for all heads
-//                  of the group and both maps (the key row is read once), fp32 throughout; the warps'
-//                  partial results (running maximum, sum, weighted values) are merged in shared memory and
-//                  written per slice; diff_merge adds the slices, subtracts, norms and stores.
+//                  of the group and both maps (the key row is read once) while the tile's value rows,
+//                  requested before, wait in registers; fp32 throughout; the warps' partial results (running
+//                  maximum, sum, weighted values) are merged in shared memory and written per slice;
+//                  diff_merge adds the slices, subtracts, norms and stores.
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
@@ -296,19 +297,38 @@ int launch_diff_prefill(const bf16* q, int q_stride, const bf16* kpages, const b
 // ---- one token per sequence: slices of the keys on the FMA pipes ------------------------------------
 constexpr int DEC_WARPS = 8;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
-constexpr int MAX_VC = 4;  // values of up to 128: 4 per lane
+constexpr int MAX_VC = 4;  // values of up to 128 (the merge kernel: 4 per lane)
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    v[2 * e] = f.x;
+    v[2 * e + 1] = f.y;
+  }
+}
 
 // mid: [num_seqs, nq, splits, 2 maps, DV + 2] floats: the weighted values, then the running maximum and sum.
-template <int G>
-__global__ void __launch_bounds__(DEC_THREADS)
+// A tile is 32 keys.  Its value rows are requested first, 16 bytes a lane (DV / 8 lanes a row, so 256 / DV rows
+// an instruction), and wait in registers while the lanes score one key each (all heads of the group, both
+// maps, the key row in rounds of 32 elements a map); so a tile costs about three memory round trips, not one
+// per key.  A warp serves GS heads of the group's G: the G / GS warps of a tile read the same rows (the second
+// from cache) and each carries a short instruction stream and few accumulators, so that two blocks fit an SM.
+// VB: value-row instructions in flight at a time.
+template <int G, int GS, int VB>
+__global__ void __launch_bounds__(DEC_THREADS, 2)
 diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpages,
                    const bf16* __restrict__ vpages, const int* __restrict__ block_table, int max_pages,
                    const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens, float* __restrict__ mid,
                    int nq, int nkv, int D, int DV, int ps, float scale, int window, int chunk, int splits) {
   extern __shared__ float dec_smem[];
   float* qs = dec_smem;                       // [G][2 D], scaled
-  float* part = dec_smem + G * 2 * D;         // [DEC_WARPS][G * 2][DV + 2]
+  float* part = dec_smem + G * 2 * D;         // [NTS][G * 2][DV + 2]
+  constexpr int WPT = G / GS;                 // warps a tile
+  constexpr int NTS = DEC_WARPS / WPT;        // tiles the block works on at a time
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ts = warp / WPT, g0 = (warp % WPT) * GS;
   const int seq = blockIdx.x / nkv, kvh = blockIdx.x - seq * nkv;
   const int split = blockIdx.y;
   const int tok = cu_seqlens[seq];
@@ -318,124 +338,132 @@ diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   const int slice = (((n + splits - 1) / splits) + 31) & ~31;
   const int k_begin = lo + split * slice, k_end = min(p + 1, k_begin + slice);
   const int* bt = block_table + (long)seq * max_pages;
-  const int KW = 2 * D, vc = DV / 32;
+  const int KW = 2 * D;
+  const int lpr = DV / 8;          // lanes a value row: 4, 8 or 16
+  const int rpi = 32 / lpr;        // value rows an instruction
+  const int col = (lane % lpr) * 8, sub = lane / lpr;
   const bf16* qrow = q + (long)tok * q_stride + (long)kvh * G * KW;
   for (int i = threadIdx.x; i < G * KW; i += DEC_THREADS) qs[i] = to_f32(qrow[i]) * scale;
   __syncthreads();
 
-  float m[G][2], l[G][2], acc[G][2][MAX_VC];
+  float m[GS][2], l[GS][2], acc[GS][2][8];
 #pragma unroll
-  for (int g = 0; g < G; ++g)
+  for (int g = 0; g < GS; ++g)
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
       m[g][w] = -INFINITY;
       l[g][w] = 0.f;
 #pragma unroll
-      for (int c = 0; c < MAX_VC; ++c) acc[g][w][c] = 0.f;
+      for (int c = 0; c < 8; ++c) acc[g][w][c] = 0.f;
     }
-  for (int j0 = k_begin + warp * 32; j0 < k_end; j0 += DEC_WARPS * 32) {
+  for (int j0 = k_begin + ts * 32; j0 < k_end; j0 += NTS * 32) {
     const int j = j0 + lane;
     const bool valid = j < k_end;
-    long row = 0;
-    float s[G][2];
+    const int count = min(32, k_end - j0);
+    const long row = valid ? ((long)bt[j / ps] * nkv + kvh) * ps + (j % ps) : 0;
+    float pw[GS][2];
 #pragma unroll
-    for (int g = 0; g < G; ++g) s[g][0] = s[g][1] = 0.f;
-    if (valid) {
-      row = ((long)bt[j / ps] * nkv + kvh) * ps + (j % ps);
-      const bf16* kr = kpages + row * KW;
-      // 32 elements of each map per round: the round's eight 16-byte loads are in flight together
-      for (int d0 = 0; d0 < D; d0 += 32) {
-        uint4 ra[4], rb[4];
+    for (int vb = 0; vb < 16; vb += VB) {  // (one pass when all of a tile's value rows fit in registers)
+      uint4 vreg[VB];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const bool in = d0 + 8 * u < D;
-          ra[u] = in ? *reinterpret_cast<const uint4*>(kr + d0 + 8 * u) : make_uint4(0, 0, 0, 0);
-          rb[u] = in ? *reinterpret_cast<const uint4*>(kr + D + d0 + 8 * u) : make_uint4(0, 0, 0, 0);
-        }
+      for (int i = 0; i < VB; ++i) {
+        const int key = (vb + i) * rpi + sub;
+        const long rj = __shfl_sync(0xffffffffu, row, key & 31);
+        vreg[i] = (vb + i) * rpi < 32 && key < count ? *reinterpret_cast<const uint4*>(vpages + rj * DV + col)
+                                                      : make_uint4(0, 0, 0, 0);
+      }
+      if (vb == 0) {
+        float s[GS][2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int d = d0 + 8 * u;
-          if (d >= D) break;
-          const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&ra[u]);
-          const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&rb[u]);
-          float ka[8], kb[8];
+        for (int g = 0; g < GS; ++g) s[g][0] = s[g][1] = 0.f;
+        if (valid) {
+          const bf16* kr = kpages + row * KW;
+          for (int d0 = 0; d0 < D; d0 += 32) {  // 32 elements of each map a round, its eight loads in flight together
+            uint4 ra[4], rb[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
-            ka[2 * e] = fa.x, ka[2 * e + 1] = fa.y, kb[2 * e] = fb.x, kb[2 * e + 1] = fb.y;
-          }
+            for (int u = 0; u < 4; ++u) {
+              const bool in = d0 + 8 * u < D;
+              ra[u] = in ? *reinterpret_cast<const uint4*>(kr + d0 + 8 * u) : make_uint4(0, 0, 0, 0);
+              rb[u] = in ? *reinterpret_cast<const uint4*>(kr + D + d0 + 8 * u) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const float* qg = qs + g * KW;
+            for (int u = 0; u < 4; ++u) {
+              const int d = d0 + 8 * u;
+              if (d >= D) break;
+              float ka[8], kb[8];
+              unpack8(ra[u], ka);
+              unpack8(rb[u], kb);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              s[g][0] = fmaf(qg[d + e], ka[e], s[g][0]);
-              s[g][1] = fmaf(qg[D + d + e], kb[e], s[g][1]);
+              for (int g = 0; g < GS; ++g) {
+                const float* qg = qs + (g0 + g) * KW;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  s[g][0] = fmaf(qg[d + e], ka[e], s[g][0]);
+                  s[g][1] = fmaf(qg[D + d + e], kb[e], s[g][1]);
+                }
+              }
             }
           }
         }
-      }
-    }
-    float pw[G][2];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const float sv = valid ? s[g][w] : -INFINITY;
-        const float m_new = fmaxf(m[g][w], warp_max(sv));
-        pw[g][w] = valid ? expf(sv - m_new) : 0.f;
-        const float corr = expf(m[g][w] - m_new);
-        l[g][w] = l[g][w] * corr + warp_sum(pw[g][w]);
-#pragma unroll
-        for (int c = 0; c < MAX_VC; ++c) acc[g][w][c] *= corr;
-        m[g][w] = m_new;
-      }
-    const int count = min(32, k_end - j0);
-    for (int j4 = 0; j4 < count; j4 += 4) {  // four keys a round: their value loads are in flight together
-      float v[4][MAX_VC];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long rj = __shfl_sync(0xffffffffu, row, j4 + u);
-        const bf16* vr = vpages + rj * DV;
-        const bool in = j4 + u < count;  // a key past the end weighs nothing and is never read
-#pragma unroll
-        for (int c = 0; c < MAX_VC; ++c) v[u][c] = in && c < vc ? to_f32(vr[lane + 32 * c]) : 0.f;
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-#pragma unroll
-        for (int g = 0; g < G; ++g)
+        for (int g = 0; g < GS; ++g)
 #pragma unroll
           for (int w = 0; w < 2; ++w) {
-            const float pj = __shfl_sync(0xffffffffu, pw[g][w], j4 + u);
+            const float sv = valid ? s[g][w] : -INFINITY;
+            const float m_new = fmaxf(m[g][w], warp_max(sv));
+            pw[g][w] = valid ? expf(sv - m_new) : 0.f;
+            const float corr = expf(m[g][w] - m_new);
+            l[g][w] = l[g][w] * corr + warp_sum(pw[g][w]);
 #pragma unroll
-            for (int c = 0; c < MAX_VC; ++c) acc[g][w][c] = fmaf(pj, v[u][c], acc[g][w][c]);
+            for (int c = 0; c < 8; ++c) acc[g][w][c] *= corr;
+            m[g][w] = m_new;
           }
+      }
+#pragma unroll
+      for (int i = 0; i < VB; ++i) {
+        const int key = ((vb + i) * rpi + sub) & 31;  // (rows past the tile were not loaded: zeros)
+        float v[8];
+        unpack8(vreg[i], v);
+#pragma unroll
+        for (int g = 0; g < GS; ++g)
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            const float pj = __shfl_sync(0xffffffffu, pw[g][w], key);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[g][w][c] = fmaf(pj, v[c], acc[g][w][c]);
+          }
+      }
     }
   }
-  // the warps' results side by side, then one warp per (head, map) merges them in warp order
+  // the lanes that hold the same columns added up, the tiles' results side by side, then one warp per
+  // (head, map) merges them in order
   const int PW = DV + 2;
 #pragma unroll
-  for (int g = 0; g < G; ++g)
+  for (int g = 0; g < GS; ++g)
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
-      float* dst = part + ((long)warp * G * 2 + g * 2 + w) * PW;
 #pragma unroll
-      for (int c = 0; c < MAX_VC; ++c)
-        if (c < vc) dst[lane + 32 * c] = acc[g][w][c];
+      for (int c = 0; c < 8; ++c)
+        for (int o = lpr; o < 32; o <<= 1) acc[g][w][c] += __shfl_xor_sync(0xffffffffu, acc[g][w][c], o);
+      float* dst = part + ((long)ts * G * 2 + (g0 + g) * 2 + w) * PW;
+      if (lane < lpr) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) dst[col + c] = acc[g][w][c];
+      }
       if (lane == 0) {
         dst[DV] = m[g][w];
         dst[DV + 1] = l[g][w];
       }
     }
   __syncthreads();
+  const int vc = DV / 32;
   for (int item = warp; item < G * 2; item += DEC_WARPS) {
     float mm = -INFINITY;
-    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, part[((long)w * G * 2 + item) * PW + DV]);
+    for (int w = 0; w < NTS; ++w) mm = fmaxf(mm, part[((long)w * G * 2 + item) * PW + DV]);
     float ll = 0.f, a[MAX_VC];
 #pragma unroll
     for (int c = 0; c < MAX_VC; ++c) a[c] = 0.f;
-    for (int w = 0; w < DEC_WARPS; ++w) {
+    for (int w = 0; w < NTS; ++w) {
       const float* src = part + ((long)w * G * 2 + item) * PW;
       const float f = src[DV] == -INFINITY ? 0.f : expf(src[DV] - mm);
       ll += f * src[DV + 1];
@@ -455,7 +483,9 @@ diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   }
 }
 
-// One warp per (sequence, head): the slices of both maps added up, the subtraction, the norm, the store.
+// One warp per (sequence, head): the slices of both maps added up, the subtraction, the norm, the store.  A
+// lane fetches one slice's maximum and sum (so all slices' are in flight at once) and the warp agrees on the
+// weights; the value loads of four slices are in flight together.  splits <= 64.
 __global__ void diff_merge_kernel(const float* __restrict__ mid, const int* __restrict__ cu_seqlens,
                                   bf16* __restrict__ out, long out_stride, int num_seqs, int nq, int DV, int splits,
                                   float lambda, float eps, float out_scale) {
@@ -464,30 +494,42 @@ __global__ void diff_merge_kernel(const float* __restrict__ mid, const int* __re
   if (item >= (long)num_seqs * nq) return;
   const int seq = (int)(item / nq), h = (int)(item - (long)seq * nq);
   const int PW = DV + 2, vc = DV / 32;
-  float a[2][MAX_VC];
+  const float* base = mid + item * splits * 2 * PW;  // [splits][2 maps][PW]
+  float f[2][2], inv[2];                               // weights of slices lane and lane + 32, per map
+#pragma unroll
   for (int w = 0; w < 2; ++w) {
-    const float* base = mid + ((item * splits) * 2 + w) * PW;
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, base[(long)s * 2 * PW + DV]);
-    float ll = 0.f;
+    float ms[2], ls[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int sl = lane + 32 * k;
+      ms[k] = sl < splits ? base[((long)sl * 2 + w) * PW + DV] : -INFINITY;
+      ls[k] = sl < splits ? base[((long)sl * 2 + w) * PW + DV + 1] : 0.f;
+    }
+    const float mm = warp_max(fmaxf(ms[0], ms[1]));
+#pragma unroll
+    for (int k = 0; k < 2; ++k) f[w][k] = ms[k] == -INFINITY ? 0.f : expf(ms[k] - mm);
+    inv[w] = 1.f / warp_sum(f[w][0] * ls[0] + f[w][1] * ls[1]);
+  }
+  float a[2][MAX_VC];
+#pragma unroll
+  for (int w = 0; w < 2; ++w)
 #pragma unroll
     for (int c = 0; c < MAX_VC; ++c) a[w][c] = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* src = base + (long)s * 2 * PW;
-      const float f = src[DV] == -INFINITY ? 0.f : expf(src[DV] - mm);
-      ll += f * src[DV + 1];
+#pragma unroll 4
+  for (int sl = 0; sl < splits; ++sl) {
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const float fs = __shfl_sync(0xffffffffu, sl < 32 ? f[w][0] : f[w][1], sl & 31);
+      const float* src = base + ((long)sl * 2 + w) * PW;
 #pragma unroll
       for (int c = 0; c < MAX_VC; ++c)
-        if (c < vc) a[w][c] += f * src[lane + 32 * c];
+        if (c < vc) a[w][c] = fmaf(fs, src[lane + 32 * c], a[w][c]);
     }
-    const float inv = 1.f / ll;
-#pragma unroll
-    for (int c = 0; c < MAX_VC; ++c) a[w][c] *= inv;
   }
   float ss = 0.f;
 #pragma unroll
   for (int c = 0; c < MAX_VC; ++c) {
-    a[0][c] = c < vc ? a[0][c] - lambda * a[1][c] : 0.f;
+    a[0][c] = c < vc ? a[0][c] * inv[0] - lambda * (a[1][c] * inv[1]) : 0.f;
     ss += a[0][c] * a[0][c];
   }
   const float rstd = rsqrtf(warp_sum(ss) / (float)DV + eps) * out_scale;
@@ -505,12 +547,13 @@ int launch_diff_decode(const bf16* q, int q_stride, const bf16* kpages, const bf
   const size_t smem = ((size_t)G * 2 * D + (size_t)DEC_WARPS * G * 2 * (DV + 2)) * sizeof(float);
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
   if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(diff_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      cudaFuncSetAttribute(diff_decode_kernel<G, (G > 2 ? 2 : G), 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
     return Q3_ERR_LAUNCH;
   dim3 grid(num_seqs * nkv, splits);
-  diff_decode_kernel<G><<<grid, DEC_THREADS, smem, stream>>>(q, q_stride, kpages, vpages, block_table, max_pages,
-                                                             kv_lens, cu_seqlens, mid, nq, nkv, D, DV, ps, scale,
-                                                             window, chunk, splits);
+  diff_decode_kernel<G, (G > 2 ? 2 : G), 8><<<grid, DEC_THREADS, smem, stream>>>(
+      q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, mid, nq, nkv, D, DV, ps, scale, window,
+      chunk, splits);
   return q3_launch_status();
 }
 
@@ -544,7 +587,7 @@ Q3_EXPORT int q3_diff_attention_prefill(const void* q, int q_stride, const void*
 }
 
 // One token per sequence (token row of sequence b: cu_seqlens[b], its position kv_lens[b] - 1).  D a multiple of
-// 8, DV a multiple of 32 up to 128, groups of 1, 2, 4 or 8 heads; mid: num_seqs * nq * splits * 2 * (DV + 2) floats.
+// 8, DV 32, 64 or 128, groups of 1, 2, 4 or 8 heads; mid: num_seqs * nq * splits * 2 * (DV + 2) floats.
 Q3_EXPORT int q3_diff_attention_decode(const void* q, int q_stride, const void* kpages, const void* vpages,
                                        const int* block_table, int max_pages, const int* kv_lens,
                                        const int* cu_seqlens, void* out, long out_stride, float* mid, int num_seqs,
@@ -552,8 +595,8 @@ Q3_EXPORT int q3_diff_attention_decode(const void* q, int q_stride, const void* 
                                        int splits, float lambda, float eps, float out_scale, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out || !mid) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_seqs < 0 || splits < 1 || chunk < 0) return Q3_ERR_ARGUMENT;
-  if (D < 8 || D % 8 || DV < 32 || DV % 32 || DV > 32 * MAX_VC || out_stride < (long)nq * DV) return Q3_ERR_UNSUPPORTED;
-  if (((uintptr_t)kpages & 15) || splits > 65535) return Q3_ERR_UNSUPPORTED;
+  if (D < 8 || D % 8 || (DV != 32 && DV != 64 && DV != 128) || out_stride < (long)nq * DV) return Q3_ERR_UNSUPPORTED;
+  if (((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15) || splits > 64) return Q3_ERR_UNSUPPORTED;
   if (num_seqs == 0) return Q3_OK;
   const int G = nq / nkv;
   int code = Q3_ERR_UNSUPPORTED;

@@ -1113,7 +1113,9 @@ class CudaOps:
                     if limit:
                         bound = min(bound, int(limit))
                 blocks = max(1, step.num_seqs * num_kv_heads)
-                splits = max(1, min(-(-bound // 256), (2 * self.SM_COUNT) // blocks, 64))
+                # a block's 8 warps work on 8 / (group / heads per warp) tiles of 32 keys at a time; two blocks an SM
+                round_keys = 32 * 8 // max(1, group // 2)
+                splits = max(1, min(-(-bound // round_keys), (2 * self.SM_COUNT) // blocks, 64))
                 mid = torch.empty(step.num_seqs * num_heads * splits * 2 * (value_dim + 2), dtype=torch.float32,
                                   device=out.device)
                 self.launches += 1  # the merge of the slices
