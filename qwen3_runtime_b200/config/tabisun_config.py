@@ -184,14 +184,22 @@ class TabisunConfig:
         if self.logit_softcap is not None and not self.logit_softcap > 0:
             raise ConfigError("logit_softcap must be positive")
         for i, layer in enumerate(self.layers):
-            j = layer.weights_of
-            if j is None:
+            if layer.weights_of is None:
                 continue
-            if not 0 <= j < len(self.layers) or j == i or self.layers[j].weights_of is not None:
-                raise ConfigError(f"layer {i}: weights_of={j} must name another layer that has tensors of its own")
-            owner = self.layers[j]
+            owner = self.layers[self.owner_of(i)]
             if (owner.type, owner.mixer, owner.ff) != (layer.type, layer.mixer, layer.ff):
-                raise ConfigError(f"layer {i}: its entry differs from layer {j}'s, whose weights it uses")
+                raise ConfigError(f"layer {i}: its entry differs from layer {self.owner_of(i)}'s, whose weights it uses")
+
+    def owner_of(self, i: int) -> int:
+        """The layer whose stored tensors layer ``i`` runs with (itself, or where its ``weights_of`` leads)."""
+        seen = {i}
+        while self.layers[i].weights_of is not None:
+            j = self.layers[i].weights_of
+            if not 0 <= j < len(self.layers) or j in seen:
+                raise ConfigError(f"layer {i}: weights_of={j} must lead to another layer that has tensors of its own")
+            seen.add(j)
+            i = j
+        return i
 
     @classmethod
     def from_hf_config(cls, raw: Mapping[str, Any]) -> "TabisunConfig":

@@ -60,8 +60,7 @@ def tabisun_spec(cfg: TabisunConfig) -> ModelSpec:
         blocks.append(PartSpec("output_norm", params))
         names.append(f"l{i}.")
     # a layer that runs another layer's weights is a second run of that block on a cache layer of its own
-    order = tuple(LayerRun(block=block_of[i if layer.weights_of is None else layer.weights_of], cache=i)
-                  for i, layer in enumerate(cfg.layers))
+    order = tuple(LayerRun(block=block_of[cfg.owner_of(i)], cache=i) for i in range(len(cfg.layers)))
     return ModelSpec(vocab_size=cfg.vocab, hidden_size=cfg.width, blocks=tuple(blocks), order=order,
                      final_norm=norm, tie_word_embeddings=False, embed_name="embed", head_name="head",
                      block_prefix="l{index}.", block_names=tuple(names), final_norm_prefix="final.norm",

@@ -1103,8 +1103,7 @@ class CudaOps:
         group = num_heads // num_kv_heads
         if (self.differential_tc and step is not None and out.dtype == torch.bfloat16 and q_stride % 8 == 0
                 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
-            if (step.decode_only and group in (1, 2, 4, 8) and map_dim % 8 == 0 and value_dim % 32 == 0
-                    and value_dim <= 128):
+            if step.decode_only and group in (1, 2, 4, 8) and map_dim % 8 == 0 and value_dim in (32, 64, 128):
                 # one token per sequence: the keys cut into slices so that about two blocks per SM work.  The
                 # count comes from an upper bound of the lengths (in a captured step: the block-table width it
                 # was captured for), never from the lengths of the moment.

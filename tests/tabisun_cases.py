@@ -359,7 +359,8 @@ def case_differential_edges(dtype, ops, device, *, chunk=12, page_size=8, heads=
         moved = float((pl.differential_core(q.double(), blind.double(), v.double(), 1.0, lam, ch, 1e-5, 0.75).float()[qi]
                        - want[qi]).abs().max())
         lo_seen = qi // ch * ch if ch else 0
-        if qi > lo_seen:  # with a single visible key every softmax is 1 whatever the scores
+        if qi > lo_seen + 1:  # with a single visible key every softmax is 1 whatever the scores; with two the
+            # other key may by chance have nearly the same value after the head's norm
             assert (moved > 0.05) == seen, "the marked key does not stand out as intended"
         k_pages = _paged(k.reshape(T, kv_heads, 2 * D), table, page_size, pages_needed + 2, dt, device)
         v_pages = _paged(v, table, page_size, pages_needed + 2, dt, device)

@@ -31,8 +31,9 @@ def test_config_round_trip_and_refusals(tmp_path):
                               (("layers", 1, "mixer", "vdim"), 8, "values are the keys"),
                               (("layers", 1, "mixer", "rot", "dims"), 26, "even and at most"),
                               (("layers", 3, "weights_of"), 3, "another layer"),
+                              (("layers", 3, "weights_of"), 9, "another layer"),
                               (("layers", 3, "weights_of"), 1, "differs from layer"),
-                              (("layers", 4, "weights_of"), 3, "tensors of its own"),
+                              (("layers", 4, "weights_of"), 3, "differs from layer"),
                               (("norm", "eps"), 0.0, "norm.eps")):
         bad = json.loads(json.dumps(raw))
         at = bad
@@ -62,6 +63,12 @@ def test_tensor_names_and_cache_layers(tmp_path):
     assert rt.storage.view(2).latent_pages.shape[-1] == 56 and rt.storage.view(4).latent_pages is not None
     blocks = rt.runner.model.blocks
     assert len(blocks) == 3 and [r.block for r in rt.runner.model.spec.order] == [0, 1, 2, 0, 2]
+    # a layer may name a layer that itself runs another's weights: both run the owner's
+    import dataclasses
+
+    cfg = tc.CONFIGS["A"]["config"]
+    chained = dataclasses.replace(cfg, layers=(*cfg.layers, dataclasses.replace(cfg.layers[3], weights_of=3)))
+    assert chained.owner_of(5) == 0 and chained.owner_of(3) == 0 and chained.owner_of(1) == 1
 
 
 def test_chunk_pages():
