@@ -4,6 +4,7 @@ on the CPU with the torch statements of the kernels and on the GPU with the kern
 from __future__ import annotations
 
 import json
+import math
 
 import torch
 
@@ -422,6 +423,45 @@ def case_capped_far_key(dtype, ops, device, *, page_size=16, heads=4, kv_heads=2
             diff = float((out.float().cpu().reshape(hi - lo, heads, D) - want[lo:hi]).abs().max())
             tol = 3e-5 if dtype == "float32" else 4e-2
             assert diff <= tol, f"capped scores, query {qi}, key {kj}, tokens {lo}..{hi}: off by {diff:.3g}"
+
+
+def case_latent_far_key_and_sink(dtype, ops, device, *, page_size=16, heads=4, rank=64, rot=16, T=330):
+    """Attention over latent rows without a window: one row hundreds of tokens back takes nearly all the weight
+    of the last query (and of one in the middle), unless the head's sink is larger still; a sink of a head that
+    sees one row only halves (or nearly removes) that row's weight.  A whole prompt, a portion of two and a
+    single decoded token over shuffled pages with NaN in unused rows."""
+    dt = TORCH[dtype]
+    gen = torch.Generator().manual_seed(31)
+    width = rank + rot
+    pages_needed = -(-T // page_size)
+    table = list(reversed(range(1, pages_needed + 1)))
+    for qi, kj, sink_of_head0 in ((T - 1, 3, -30.0), (T - 1, T - 1 - 2 * page_size, 0.0), (T // 2, 0, 40.0)):
+        rows = 0.3 * torch.randn((T, width), generator=gen)
+        q = 0.3 * torch.randn((T, heads, width), generator=gen)
+        rows[kj, rank - 2] += 7.0
+        q[qi, :, rank - 2] += 7.0
+        rows, q = rows.to(torch.bfloat16).float(), q.to(torch.bfloat16).float()
+        sink = torch.tensor([sink_of_head0] + [0.5 * h for h in range(1, heads)])
+        scores = torch.einsum("ihd,jd->hij", q.double(), rows.double()) * 0.5
+        w = pl.softmax_rows(scores, pl.causal(T), sink=sink.double())
+        want = torch.einsum("hij,jd->ihd", w, rows[:, :rank].double()).float()
+        on_key = float((want[qi, 1] - rows[kj, :rank]).abs().max())
+        assert on_key < 0.05, "the marked row does not stand out as intended"
+        if sink_of_head0 > 30:  # a sink larger than the marked score leaves that head next to nothing
+            assert float(want[qi, 0].abs().max()) < 0.05
+        assert abs(float(w[1, 0, 0]) - 1 / (1 + math.exp(0.5 - float(scores[1, 0, 0])))) < 1e-9  # token 0: itself and the sink
+        pages = torch.full((pages_needed + 2, page_size, width), float("nan"), dtype=dt, device=device)
+        for j in range(T):
+            pages[table[j // page_size], j % page_size] = rows[j].to(dt)
+        for lo, hi in ((0, T), (qi - 1, qi + 1), (qi, qi + 1), (0, 1)):
+            step = _step(list(range(lo, hi)), [0] * (hi - lo), [table], device)
+            out = torch.zeros((hi - lo, heads, rank), dtype=dt, device=device)
+            ops.latent_attention(q[lo:hi].to(device=device, dtype=dt).contiguous(), pages=pages, value_dim=rank,
+                                 block_table=step.block_tables[0], token_seq=step.token_seq, positions=step.positions,
+                                 sink=sink.to(device), out=out, page_size=page_size, scale=0.5, window=None, step=step)
+            diff = float((out.float().cpu() - want[lo:hi]).abs().max())
+            tol = 3e-5 if dtype == "float32" else 4e-2
+            assert diff <= tol, f"latent rows, query {qi}, row {kj}, tokens {lo}..{hi}: off by {diff:.3g}"
 
 
 def case_layer_norms(dtype, ops, device):

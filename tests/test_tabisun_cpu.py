@@ -124,6 +124,7 @@ def test_attention_edges():
     tc.case_differential_edges("float32", OPS, DEV, chunk=8, page_size=8, heads=1, kv_heads=1, D=20, Dv=8)
     tc.case_capped_far_key("float32", OPS, DEV, T=130)
     tc.case_capped_far_key("float32", OPS, DEV, T=130, chunk=48)
+    tc.case_latent_far_key_and_sink("float32", OPS, DEV, T=130)
 
 
 def test_norms_and_rotations():

@@ -62,6 +62,8 @@ def test_attention_edges(ops, dtype):
     tc.case_capped_far_key(dtype, ops, DEV, chunk=100)
     tc.case_capped_far_key(dtype, ops, DEV, heads=8, kv_heads=2, D=64, T=400)
     tc.case_capped_far_key(dtype, ops, DEV, heads=4, kv_heads=1, D=128, T=400, softcap=5.0)
+    tc.case_latent_far_key_and_sink(dtype, ops, DEV)
+    tc.case_latent_far_key_and_sink(dtype, ops, DEV, page_size=8, heads=3, rank=44, rot=12, T=200)  # the general kernel
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
