@@ -560,7 +560,7 @@ int launch_diff_decode(const bf16* q, int q_stride, const bf16* kpages, const bf
 }  // namespace
 
 // Prompt portions (any mix of sequences): num_work = sum over the sequences of ceil(q_len * (nq / nkv) / 128).
-// Map sizes and value sizes (D, DV) in {(32, 64), (64, 64), (64, 128), (128, 128)}; anything else answers
+// Map sizes D of 32, 64 or 128 with value sizes DV of 64 or 128; anything else answers
 // "unsupported" and belongs on the general kernel.  out: rows out_stride elements apart, head h at column h * DV.
 Q3_EXPORT int q3_diff_attention_prefill(const void* q, int q_stride, const void* kpages, const void* vpages,
                                         const int* block_table, int max_pages, const int* kv_lens,
@@ -579,8 +579,10 @@ Q3_EXPORT int q3_diff_attention_prefill(const void* q, int q_stride, const void*
                                       num_seqs, num_work, nq, nkv, ps, scale, window, chunk, lambda, eps,          \
                                       out_scale, stream);
   Q3_DIFF_CASE(32, 64)
+  Q3_DIFF_CASE(32, 128)
   Q3_DIFF_CASE(64, 64)
   Q3_DIFF_CASE(64, 128)
+  Q3_DIFF_CASE(128, 64)
   Q3_DIFF_CASE(128, 128)
 #undef Q3_DIFF_CASE
   return Q3_ERR_UNSUPPORTED;

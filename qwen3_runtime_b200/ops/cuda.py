@@ -1124,7 +1124,7 @@ class CudaOps:
                            step.num_seqs, num_heads, num_kv_heads, map_dim, value_dim, page_size, float(scale),
                            int(window or 0), int(chunk or 0), splits, float(lam), float(eps), float(out_scale))
                 return out
-            if (map_dim, value_dim) in ((32, 64), (64, 64), (64, 128), (128, 128)):
+            if map_dim in (32, 64, 128) and value_dim in (64, 128):
                 cu = step.host_cu_seqlens
                 work = sum(-(-(cu[b + 1] - cu[b]) * group // 128) for b in range(step.num_seqs) if cu[b + 1] > cu[b])
                 self._call("attention_diff", "q3_diff_attention_prefill", "differential_attention_tc", _ptr(q),

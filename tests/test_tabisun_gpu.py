@@ -55,6 +55,8 @@ def test_attention_edges(ops, dtype):
     tc.case_differential_edges(dtype, ops, DEV, chunk=200, page_size=16, heads=8, kv_heads=1, D=32, Dv=64, T=700)
     tc.case_differential_edges(dtype, ops, DEV, chunk=100, page_size=8, heads=4, kv_heads=2, D=64, Dv=64, T=330)
     tc.case_differential_edges(dtype, ops, DEV, chunk=129, page_size=32, heads=2, kv_heads=2, D=128, Dv=128, T=420)
+    tc.case_differential_edges(dtype, ops, DEV, chunk=70, page_size=16, heads=4, kv_heads=2, D=32, Dv=128, T=230)
+    tc.case_differential_edges(dtype, ops, DEV, chunk=70, page_size=16, heads=2, kv_heads=1, D=128, Dv=64, T=230)
     # sizes that those kernels refuse although their groups and alignments fit: the general kernel serves them
     tc.case_differential_edges(dtype, ops, DEV, chunk=40, page_size=16, heads=4, kv_heads=1, D=16, Dv=96, T=130)
     tc.case_differential_edges(dtype, ops, DEV, chunk=40, page_size=16, heads=2, kv_heads=1, D=64, Dv=256, T=130)
