@@ -30,7 +30,8 @@ namespace {
 // What the fused variant needs to make q, k and v of the newest token itself, from the raw
 // output of the q/k/v projection (row layout: nq q heads, nkv k heads, nkv v heads of D):
 // per-head RMSNorm weights (null: no norm), rotation tables [max_pos, D/2] (null: none) and which
-// elements form a rotation pair (rotary.cuh).
+// elements form a rotation pair (rotary.cuh).  v_from_k: there are no v heads in the row; the value of a
+// key head is that head as projected (before norm and rotation).
 struct NewToken {
   const float* q_w;
   const float* k_w;
@@ -41,6 +42,7 @@ struct NewToken {
   float eps;
   int max_pos;
   int pairing;
+  int v_from_k;
 };
 
 // What some designs add to the attention.  keep: with a window, the sequence's first `keep` tokens stay
@@ -319,7 +321,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
       const bool live = item < items;
       const bool is_q = item < G, is_v = item == G + 1;
       const bf16* x = row + (is_q ? (long)(kvh * G + item) * D
-                                  : (long)(nq + (is_v ? nkv : 0) + kvh) * D);
+                                  : (long)(nq + (is_v && !nt.v_from_k ? nkv : 0) + kvh) * D);
       float a[8], b[8];
       if (live) {
         load8(x + 8 * c, a);
@@ -689,7 +691,8 @@ Q3_EXPORT int q3_paged_attention_decode_sink(const void* q, int q_stride, const 
 // back.  `error_word` (may be null) is set to Q3_ERR_POSITION if a newest position lies beyond
 // the tables; that token is then left unrotated and the result is invalid.
 // (keep_first, has_sink, sink, gate, gate_stride, softcap: as in q3_paged_attention_decode_sink; softcap: scores
-// become softcap * tanh(score / softcap) after the scale, 0 for none.)
+// become softcap * tanh(score / softcap) after the scale, 0 for none.  v_from_k: rows hold nq + nkv heads only and
+// a key head as projected is also its value.)
 Q3_EXPORT int q3_paged_attention_decode_fused_sink(const void* qkv, int q_stride, void* kpages, void* vpages,
                                                    const int* block_table, int max_pages, const int* kv_lens,
                                                    const int* cu_seqlens, const int* seq_list, void* out,
@@ -699,13 +702,13 @@ Q3_EXPORT int q3_paged_attention_decode_fused_sink(const void* qkv, int q_stride
                                                    const float* sin_t, int max_pos, int pairing, int* error_word,
                                                    int* tickets, const int* longest_len, int keep_first, int has_sink,
                                                    float sink, const void* gate, int gate_stride, float softcap,
-                                                   cudaStream_t stream) {
+                                                   int v_from_k, cudaStream_t stream) {
   if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
   if (keep_first < 0 || (gate && gate_stride < nq * D) || softcap < 0.f || !(scale > 0.f)) return Q3_ERR_ARGUMENT;
   const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
                          (uintptr_t)cos_t | (uintptr_t)sin_t;
   if (bits & 15) return Q3_ERR_UNSUPPORTED;
-  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing};
+  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing, v_from_k ? 1 : 0};
   Extras ex;
   ex.cap_raw = softcap / scale;
   ex.keep = window > 0 ? keep_first : 0;
@@ -728,7 +731,7 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
   return q3_paged_attention_decode_fused_sink(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens,
                                               cu_seqlens, seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale,
                                               window, num_splits, q_w, k_w, eps, cos_t, sin_t, max_pos, pairing,
-                                              error_word, tickets, longest_len, 0, 0, 0.f, nullptr, 0, 0.f, stream);
+                                              error_word, tickets, longest_len, 0, 0, 0.f, nullptr, 0, 0.f, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -168,7 +168,7 @@ _SIGNATURES = {
                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
                                                  c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                 c_int, c_float, c_void_p, c_int, c_float, c_void_p],
+                                                 c_int, c_float, c_void_p, c_int, c_float, c_int, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -1237,9 +1237,10 @@ class CudaOps:
                                max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None,
                                merge_kernel=False, longest=None, keep_first=0, sink=None, gate=None, softcap=None):
         """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
-        ``new_token`` (q_weight, k_weight, eps, cos, sin, optionally pairing): ``q`` is the raw q/k/v
-        projection and the kernel also does the work of :meth:`qk_norm_rope_store` for the newest
-        position of each sequence, ``kv_lens - 1``.  The slices of a sequence and kv head are merged
+        ``new_token`` (q_weight, k_weight, eps, cos, sin, optionally pairing and values_are_keys): ``q`` is
+        the raw q/k/v projection (q/k only with values_are_keys: a key head as projected is its value) and the
+        kernel also does the work of :meth:`qk_norm_rope_store` for the newest position of each sequence,
+        ``kv_lens - 1``.  The slices of a sequence and kv head are merged
         by whichever of their blocks finishes last (a ticket word per pair); ``merge_kernel=True``
         asks for the second kernel that callers without ticket words get (the bits are the same).
         ``num_splits`` is the slice count of the longest sequence (a shorter one gets fewer slices of
@@ -1276,7 +1277,8 @@ class CudaOps:
                        _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
                        self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets), _ptr(longest),
                        keep_first, int(sink is not None), float(sink or 0.0), _ptr(gate),
-                       gate.stride(0) if gate is not None else 0, float(softcap or 0.0))
+                       gate.stride(0) if gate is not None else 0, float(softcap or 0.0),
+                       int(bool(new_token.get("values_are_keys"))))
             return out
         self._call("attention_decode", "q3_paged_attention_decode_sink", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],

@@ -65,6 +65,7 @@ class SinkWindowAttention(Part):
         elif self.position.style != "none":
             raise ValueError(f"sink_window_attention has no {self.position.style!r} position encoding")
         self.in_weight = self.o_weight = self.q_norm = self.k_norm = None
+        self._tables = None
         self.starts: list[int] = []
 
     def param_specs(self):
@@ -105,6 +106,29 @@ class SinkWindowAttention(Part):
         return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128, 256)
                 and self.num_heads // self.num_kv_heads <= 16 and not self.chunk)
 
+    # positions for which the decode kernel that also makes the newest token's q and k keeps rotation tables;
+    # steps that reach beyond run the q/k kernel (which needs none) and the plain decode kernel
+    FUSED_POSITIONS = 32768
+
+    def _fused_tables(self):
+        """cos and sin ``[FUSED_POSITIONS, dim / 2]`` for the decode kernel that norms, turns and stores the newest
+        token itself: the part's frequencies followed by zeros (pairs that do not turn), times the magnitude.
+        None when this rotation cannot be put that way (halves pairing over a part of the head)."""
+        if self._tables is None:
+            pos = self.position
+            inv = pos.inverse_frequencies()
+            if pos.pairing == "half" and 2 * inv.numel() != self.dim:
+                self._tables = False
+            else:
+                padded = torch.zeros(self.dim // 2, dtype=torch.float32, device=inv.device)
+                padded[: inv.numel()] = inv
+                cos, sin = self.ops.rope_table(padded, self.FUSED_POSITIONS)
+                magnitude = float(getattr(pos, "magnitude", 1.0))
+                if magnitude != 1.0:
+                    cos, sin = cos * magnitude, sin * magnitude
+                self._tables = (cos, sin)
+        return self._tables or None
+
     def _slices_key(self):
         reach = self.window + self.keep_first if self.window else None  # the most keys a token sees
         return ("decode_slices", self.num_kv_heads, self.dim, reach)
@@ -134,12 +158,19 @@ class SinkWindowAttention(Part):
         gate = proj[:, s[3]:s[3] + H * Dv] if self.gate else None
         fusable = getattr(ops, "decode_new_token_ok", None)
         rotary = self.position.style == "rotary"
-        if (fusable is not None and step.decode_only and cache.writes and self._specialised() and not rotary
-                and not self.values_are_keys and not self.softcap
-                and s[1] == H * D and s[2] == (H + G) * D  # q, k and v heads side by side, as that kernel reads them
-                and fusable(proj, num_heads=H, num_kv_heads=G, head_dim=D, cos=None, q_weight=self.q_norm,
+        tables = None
+        if (fusable is not None and step.decode_only and cache.writes and self._specialised() and rotary
+                and (step.captured_width * cache.page_size or step.max_kv_len) <= self.FUSED_POSITIONS):
+            tables = self._fused_tables()
+        cos, sin = tables if tables is not None else (None, None)
+        if (fusable is not None and step.decode_only and cache.writes and self._specialised()
+                and (not rotary or tables is not None)
+                # q, k and v heads side by side, as that kernel reads them (v where k is, if the values are the keys)
+                and s[1] == H * D and s[2] == (H * D if self.values_are_keys else (H + G) * D)
+                and fusable(proj, num_heads=H, num_kv_heads=G, head_dim=D, cos=cos, q_weight=self.q_norm,
                             k_weight=self.k_norm)):
-            # one kernel: unit norm of the newest q and k, cache write, split-KV attention with sink and gate
+            # one kernel: norm (and rotation) of the newest q and k, cache write, split-KV attention with sink, gate
+            # and capped scores
             width = step.captured_width
             ops.paged_attention_decode(
                 proj, proj.stride(0), num_heads=H, num_kv_heads=G, head_dim=D, k_pages=cache.k_pages,
@@ -147,9 +178,11 @@ class SinkWindowAttention(Part):
                 out=ctx, page_size=cache.page_size, scale=self.scale, window=self.window, num_seqs=step.num_seqs,
                 max_kv_len=width * cache.page_size or step.max_kv_len,
                 new_token=dict(q_weight=self.q_norm, k_weight=self.k_norm,
-                               eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos=None, sin=None),
+                               eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos=cos, sin=sin,
+                               pairing=getattr(self.position, "pairing", "half"),
+                               values_are_keys=self.values_are_keys),
                 num_splits=step.choices.get(self._slices_key()), longest=step.kv_longest, step=step,
-                keep_first=self.keep_first, sink=self.sink, gate=gate)
+                keep_first=self.keep_first, sink=self.sink, gate=gate, softcap=self.softcap)
             return ops.linear(ctx, self.o_weight)
         ops.qk_norm_store(proj, num_heads=H, num_kv_heads=G, head_dim=D, value_dim=Dv, k_start=s[1], v_start=s[2],
                           q_weight=self.q_norm, k_weight=self.k_norm,

@@ -112,6 +112,37 @@ def test_greedy_generation_under_the_scheduler(tmp_path, ops, dtype, cuda_graph)
     tc.case_greedy_generation(tmp_path, "D", dtype, ops, DEV, cuda_graph=cuda_graph)
 
 
+def test_bfloat16_steps_take_the_specialised_kernels(tmp_path, ops):
+    """With sizes they take, a bfloat16 model runs prompt portions on the tensor-core kernels and decode steps on
+    the sliced differential kernel, the split-KV kernel in the form that also norms, turns and stores the newest
+    token (its values read where its keys are) and the tensor-core kernel over latent rows."""
+    from helpers import run_trace, trace_tail_decode
+
+    folder = tc.make_dir(tmp_path, "D")
+    launched, new_tokens = [], []
+    call, decode = ops._call, ops.paged_attention_decode
+
+    def call_spy(group, name, what, *args):
+        launched.append(what)
+        return call(group, name, what, *args)
+
+    def decode_spy(*args, **kw):
+        new_tokens.append(kw.get("new_token"))
+        return decode(*args, **kw)
+
+    ops._call, ops.paged_attention_decode = call_spy, decode_spy
+    try:
+        rt = tc.runtime(folder, "D", "bfloat16", ops, DEV, pages=16)
+        run_trace(rt, trace_tail_decode(tc.requests_for("D", (70,)), tail=5))
+    finally:
+        del ops._call, ops.paged_attention_decode
+    for kernel in ("differential_attention_tc", "differential_attention_decode", "paged_attention_prefill",
+                   "paged_attention_decode_fused", "latent_attention_tc"):
+        assert kernel in launched, f"{kernel} was not launched: {sorted(set(launched))}"
+    assert "differential_attention" not in launched and "paged_attention" not in launched  # the general kernels
+    assert new_tokens and all(nt is not None and nt["values_are_keys"] and nt["cos"] is not None for nt in new_tokens)
+
+
 def test_trace_replay_program_on_a_tabisun_folder(tmp_path, ops):
     """bin/trace_run as a subprocess: the model class is chosen by config.json."""
     import json
